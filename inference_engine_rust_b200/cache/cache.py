@@ -30,6 +30,7 @@ class KVRequest:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: every earlier key stays visible
+    values: bool = True              # False: one row per position (keys only), e.g. a shared latent
 
 
 @dataclass(frozen=True)
@@ -61,7 +62,7 @@ class KVGroup:
             self.ring_pages = min(self.table_width, max(1, math.ceil(req.window / page_tokens)))
         shape = (len(self.layers), n_pages, req.kv_heads, page_tokens, req.head_dim)
         self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        self.v = torch.empty(shape if req.values else (len(self.layers), 0) + shape[2:], dtype=dtype, device=device)
         self.poison = poison
         if poison:
             self.k.fill_(float("nan"))
@@ -104,7 +105,8 @@ class KVGroup:
         if self.poison and pages:
             idx = torch.tensor(pages, dtype=torch.long, device=self.device)
             self.k[:, idx] = float("nan")
-            self.v[:, idx] = float("nan")
+            if self.req.values:
+                self.v[:, idx] = float("nan")
         self.table_host[slot, :] = -1
         self._dirty.add(slot)
 
@@ -129,7 +131,7 @@ class KVGroup:
         return list(self._pages_of[slot])
 
     def bytes_per_token(self) -> int:
-        return 2 * len(self.layers) * self.req.kv_heads * self.req.head_dim * self.k.element_size()
+        return (2 if self.req.values else 1) * len(self.layers) * self.req.kv_heads * self.req.head_dim * self.k.element_size()
 
 
 class StateGroup:
@@ -223,7 +225,7 @@ class Cache:
         if self.device.type != "cuda":
             return None
         from ..csrc import bindings as B
-        return B.KvView(k=g.k[i].data_ptr(), v=g.v[i].data_ptr(), page_table=g.table.data_ptr(),
+        return B.KvView(k=g.k[i].data_ptr(), v=g.v[i].data_ptr() if g.req.values else None, page_table=g.table.data_ptr(),
                         table_width=g.table_width, ring_pages=g.ring_pages, page_tokens=g.page_tokens,
                         n_pages=g.n_pages, kv_heads=g.req.kv_heads, head_dim=g.req.head_dim,
                         dtype=B.dtype_code(g.dtype), window=g.req.window or 0)

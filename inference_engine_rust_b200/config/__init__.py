@@ -4,10 +4,11 @@ from .registry import (ConfigError, architecture, architecture_name_of, config_f
                        register_architecture, spec_of)
 from .specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .mistral import MistralConfig  # registers "MistralForCausalLM"
+from .vefulix import VefulixConfig  # registers "Vefulix"
 from .presets import PRESETS, preset
 
 __all__ = [
     "ConfigError", "architecture", "architecture_name_of", "config_from_dict",
     "known_architectures", "load_config", "read_config_json", "register_architecture",
-    "spec_of", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "MistralConfig", "PRESETS", "preset",
+    "spec_of", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "MistralConfig", "VefulixConfig", "PRESETS", "preset",
 ]

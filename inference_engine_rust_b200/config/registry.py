@@ -49,6 +49,10 @@ def architecture(name: str) -> ArchitectureEntry:
 
 
 def architecture_name_of(raw: Mapping[str, Any]) -> str:
+    """The name a config.json gives its architecture: `architectures[0]`, or the single string
+    `architecture`."""
+    if "architectures" not in raw and isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
     archs = raw.get("architectures")
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
         raise ConfigError("config.json: key 'architectures' must be a non-empty list of names")

@@ -45,6 +45,7 @@ class LayerSpec:
     mixer_norm_name: str       # e.g. "model.layers.3.input_layernorm.weight"
     ffn_norm_name: str         # e.g. "model.layers.3.post_attention_layernorm.weight"
     extra_norms: Mapping[str, Tuple[PartSpec, str]] = field(default_factory=dict)
+    block_prefix: str = ""     # where the block arrangement finds tensors of its own, if it has any
 
 
 @dataclass(frozen=True)
@@ -81,6 +82,10 @@ class ModelSpec:
     # Parts that run once per step, after the embedding and before the first block: (spec, tensor-name prefix).
     # Each may change the embedded rows and publish tensors for the blocks (a per-layer input, say).
     inputs: Sequence[Tuple[PartSpec, str]] = ()
+    # None: one residual row per token.  S: the residual is kept as S parallel streams per token
+    # ([tokens, S, hidden], all equal to the embedded row at the start, summed before the final norm);
+    # the blocks of such a model take the streams, and the norms need `forward_streams`.
+    residual_streams: Optional[int] = None
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -105,6 +105,22 @@ def _declare(lib) -> None:
         "iert_gemm_tc": [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int,
                          P, c_longlong, P, c_int, c_int, c_int, c_int, P, S],
     }
+    LL = c_longlong
+    sigs.update({
+        "iert_streams_norm": [P, c_int, c_int, P, P, P, c_int, c_int, c_int, P, P, P, c_float, P, c_int, P, P, c_int, S],
+        "iert_streams_expand": [P, P, c_int, c_int, c_int, S],
+        "iert_softcap": [P, LL, c_float, S],
+        "iert_delta_prep": [P, c_int, LL, P, LL, P, P, P, P, LL, LL, P, P, P, c_int, c_int, c_int, c_int, c_int,
+                            POINTER(BatchView), S],
+        "iert_gated_head_norm": [P, P, c_int, LL, c_int, P, c_int, c_int, c_float, P, c_int, c_int, c_int, S],
+        "iert_latent_norm_store": [P, LL, c_int, c_int, P, P, c_float, P, P, c_int, POINTER(BatchView), POINTER(KvView),
+                                   c_int, P, S],
+        "iert_latent_attention_prompt": [P, LL, P, c_int, POINTER(BatchView), c_int, c_int, c_int, c_float, P, S],
+        "iert_latent_attention_decode": [P, LL, P, P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_int, c_int,
+                                         c_float, P, P, S],
+        "iert_router_topk": [P, LL, P, c_int, c_int, c_int, P, P, P, S],
+        "iert_moe_scale": [P, c_int, LL, P, c_int, c_int, c_int, S],
+    })
     lib.iert_attention_decode.argtypes = [P, P, POINTER(BatchView), POINTER(KvView), c_int, c_float, c_int, P, P, S]
     lib.iert_attention_decode.restype = c_int
     lib.iert_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
@@ -509,3 +525,133 @@ def gemm_tc_gated(x, w, act, M: int, err, stream, force_bt: int = 0, force_stage
         return False
     check(status, "gemm_tc_gated")
     return True
+
+
+# ---------------------------------------------------------------------------------------
+# streams of the residual, LayerNorm, soft cap
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def streams_norm(xs, S: int, H: int, rows: int, stream, *, y=None, mix=None, outc=None, update: bool = False,
+                 write_back: bool = False, zero_y: bool = False, in_coef=None, w=None, b=None, eps: float = 0.0,
+                 out=None, sum_out=None, rows_idx=None) -> None:
+    """One pass over the S fp32 streams `xs` [T, S, H] of `rows` token rows: optional update with a
+    sublayer's output `y` (x'_t = sum_s mix[s, t] x_s + outc[t] y; `write_back` stores it), optional
+    clearing of y's rows, the combination u = sum_s in_coef[s] x'_s (ones when None), and LayerNorm
+    of u with weight `w` and bias `b` into `out` (and / or u itself into `sum_out`).  `rows_idx`
+    gathers token rows.  Small vectors are fp32."""
+    check(core().iert_streams_norm(xs.data_ptr(), S, H, _ptr(y), _ptr(mix), _ptr(outc), 1 if update else 0,
+                                   1 if write_back else 0, 1 if zero_y else 0, _ptr(in_coef), _ptr(w), _ptr(b), eps,
+                                   _ptr(out), dtype_code(out.dtype) if out is not None else F32, _ptr(sum_out),
+                                   _ptr(rows_idx), rows, stream), "streams_norm")
+
+
+def streams_expand(x, xs, n_tokens: int, S: int, H: int, stream) -> None:
+    check(core().iert_streams_expand(x.data_ptr(), xs.data_ptr(), n_tokens, S, H, stream), "streams_expand")
+
+
+def softcap(z, cap: float, stream) -> None:
+    check(core().iert_softcap(z.data_ptr(), z.numel(), cap, stream), "softcap")
+
+
+# ---------------------------------------------------------------------------------------
+# recurrent mixers
+
+
+def delta_prep(proj, gates, conv_w, A_log, dt_bias, state, conv_off: int, qkv, beta, decay, G: int, D: int, H: int,
+               V: int, taps: int, batch: BatchView, stream) -> None:
+    check(core().iert_delta_prep(proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), gates.data_ptr(), gates.stride(0),
+                                 conv_w.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), state.stride(0),
+                                 conv_off, qkv.data_ptr(), beta.data_ptr(), decay.data_ptr(), G, D, H, V, taps,
+                                 byref(batch), stream), "delta_prep")
+
+
+def gated_head_norm(o, proj, gate_off: int, w, per_head: bool, act: int, eps: float, out, n_tokens: int, H: int, V: int,
+                    stream) -> None:
+    """out[t, h, :] = o[t, h, :] / rms * w * act(gate): act 0 = SiLU, 1 = sigmoid; `per_head`: w is one
+    vector of V shared by the heads, else H*V."""
+    check(core().iert_gated_head_norm(o.data_ptr(), proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), gate_off,
+                                      w.data_ptr(), 1 if per_head else 0, act, eps, out.data_ptr(), n_tokens, H, V, stream),
+          "gated_head_norm")
+
+
+_recurrent_libs = {}
+
+
+def _recurrent_lib(dim: int):
+    """The recurrence library for one key size, compiled on first use."""
+    lib = _recurrent_libs.get(dim)
+    if lib is None:
+        lib = build.load_library(*build.recurrent_library(dim))
+        P, LL = c_void_p, c_longlong
+        lib.iert_delta_recur.argtypes = [P, P, P, P, LL, LL, P, c_int, c_int, c_int, POINTER(BatchView), P]
+        lib.iert_delta_recur.restype = c_int
+        lib.iert_mlstm_recur.argtypes = [P, c_int, LL, P, LL, P, P, c_float, P, LL, LL, LL, LL, P, P, c_int, c_int,
+                                         POINTER(BatchView), P]
+        lib.iert_mlstm_recur.restype = c_int
+        if os.environ.get("IERT_PDL", "1") == "0":
+            lib.iert_set_pdl(0)
+        _recurrent_libs[dim] = lib
+    return lib
+
+
+def _check_lib(status: int, what: str, launches: int = 1) -> None:
+    global launch_count
+    if status == 1:
+        raise KernelError(f"{what}: the kernel does not take these sizes or options")
+    if status != 0:
+        raise KernelError(f"{what}: the launch failed")
+    launch_count += launches
+
+
+def delta_recur(qkv, beta, decay, state, s_off: int, o, G: int, D: int, H: int, V: int, batch: BatchView, stream) -> None:
+    """The gated delta rule over the step's tokens, state [slots, floats] read and written at `s_off`."""
+    _check_lib(_recurrent_lib(D).iert_delta_recur(qkv.data_ptr(), beta.data_ptr(), decay.data_ptr(), state.data_ptr(),
+                                                  state.stride(0), s_off, o.data_ptr(), G, H, V, byref(batch), stream),
+               "delta_recur")
+
+
+def mlstm_recur(proj, gates, bi, bf, cap: float, state, s_off: int, n_off: int, m_off: int, coef, o, D: int, H: int, V: int,
+                batch: BatchView, stream) -> None:
+    """The mLSTM recurrence over the step's tokens (a scan of the gates and the normaliser, then the
+    matrix state by columns)."""
+    _check_lib(_recurrent_lib(D).iert_mlstm_recur(proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), gates.data_ptr(),
+                                                  gates.stride(0), bi.data_ptr(), bf.data_ptr(), cap, state.data_ptr(),
+                                                  state.stride(0), s_off, n_off, m_off, coef.data_ptr(), o.data_ptr(), H, V,
+                                                  byref(batch), stream), "mlstm_recur", 2)
+
+
+# ---------------------------------------------------------------------------------------
+# latent attention, routing
+
+
+def latent_norm_store(x, q_rank: int, kv_rank: int, wq, wkv, eps: float, cq, c, batch: BatchView, kv: KvView, store: bool,
+                      err, stream) -> None:
+    check(core().iert_latent_norm_store(x.data_ptr(), x.stride(0), q_rank, kv_rank, wq.data_ptr(), wkv.data_ptr(), eps,
+                                        cq.data_ptr(), c.data_ptr(), dtype_code(c.dtype), byref(batch), byref(kv),
+                                        1 if store else 0, err.data_ptr(), stream), "latent_norm_store")
+
+
+def latent_attention_prompt(qkv, out, batch: BatchView, H: int, D: int, V: int, scale: float, sink, stream) -> None:
+    check(core().iert_latent_attention_prompt(qkv.data_ptr(), qkv.stride(0), out.data_ptr(), dtype_code(qkv.dtype),
+                                              byref(batch), H, D, V, scale, _ptr(sink), stream), "latent_attention_prompt")
+
+
+def latent_attention_decode(q, w_uk, w_uv, out, batch: BatchView, kv: KvView, H: int, D: int, V: int, scale: float, sink,
+                            err, stream) -> None:
+    check(core().iert_latent_attention_decode(q.data_ptr(), q.stride(0), w_uk.data_ptr(), w_uv.data_ptr(), out.data_ptr(),
+                                              dtype_code(q.dtype), byref(batch), byref(kv), H, D, V, scale, _ptr(sink),
+                                              err.data_ptr(), stream), "latent_attention_decode")
+
+
+def router_topk(z, bias, n_tokens: int, E: int, top: int, wt, idx, w, stream) -> None:
+    check(core().iert_router_topk(z.data_ptr(), z.stride(0), _ptr(bias), n_tokens, E, top, wt.data_ptr(), idx.data_ptr(),
+                                  w.data_ptr(), stream), "router_topk")
+
+
+def moe_scale(act, wt, n_tokens: int, E: int, F: int, stream) -> None:
+    check(core().iert_moe_scale(act.data_ptr(), dtype_code(act.dtype), act.stride(0), wt.data_ptr(), n_tokens, E, F, stream),
+          "moe_scale")

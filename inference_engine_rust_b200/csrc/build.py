@@ -35,6 +35,7 @@ NVCC_FLAGS = [
 CORE_SOURCES = [
     "runtime.cu", "elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu",
     "gemm_tc.cu", "gemm_rows.cu", "attention_decode.cu",
+    "streams_norm.cu", "recurrent_prep.cu", "latent_attention.cu", "moe.cu",
 ]
 # the native reader of weight files (host code), loaded by the weights package
 IO_SOURCES = ["weight_reader.cu"]
@@ -181,6 +182,17 @@ def attention_library(head_dim: int):
             [f"HEAD_DIM={head_dim}"])
 
 
+# Key sizes whose recurrence library is built ahead of time by build_all(); any other size is compiled
+# the first time a model with that size runs.
+PREBUILT_RECURRENT_DIMS = (64, 128)
+
+
+def recurrent_library(dim: int):
+    """(name, sources, defines) of the matrix-state recurrences (gated delta rule, mLSTM) for one key
+    size: a thread keeps its rows of the state in registers, so the size is a compile-time constant."""
+    return (f"iert_recurrent_d{dim}", ["runtime.cu", "recurrent.cu"], [f"DIM={dim}"])
+
+
 def build_all(verbose: bool = True) -> List[str]:
     """Every library the package can need that does not depend on a model's sizes, plus the
     size-specialised ones for the head sizes in `PREBUILT_HEAD_DIMS`."""
@@ -188,4 +200,6 @@ def build_all(verbose: bool = True) -> List[str]:
              build_library("iert_io", IO_SOURCES, verbose=verbose)]
     for hd in PREBUILT_HEAD_DIMS:
         paths.append(build_library(*attention_library(hd), verbose=verbose))
+    for d in PREBUILT_RECURRENT_DIMS:
+        paths.append(build_library(*recurrent_library(d), verbose=verbose))
     return paths

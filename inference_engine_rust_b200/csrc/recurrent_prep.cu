@@ -1,0 +1,145 @@
+// Kernels around the recurrent mixers that do not depend on the state's sizes at compile time.
+//
+// delta_prep: what the gated delta rule needs per token, from the packed projection of the step:
+//   short causal convolution per channel (taps along time, the last column is the current token's,
+//   zeros before the sequence's start) + SiLU on the q, k and v channels; q and k made unit vectors
+//   per head, x / sqrt(sum x^2 + 1e-6), q also times dim^-1/2; beta = sigmoid(b); the decay
+//   g = exp(-exp(A_log) * softplus(a + dt_bias)).  Everything after the projection is fp32.
+//   The convolution's history lives in the sequence's state as a ring of `taps` rows: the input of
+//   position p is kept in row p % taps, so a step reads rows of earlier positions while it writes
+//   its own.  (A step brings either a whole prompt from position 0, which reads no history, or one
+//   token, which writes one row and reads the others: no row is read and written in one launch.)
+//
+// gated_head_norm: each head's read-out divided by its root mean square (eps inside the root),
+//   times a weight, times an activation of the gate projection, stored in the run's dtype.
+#include "common.cuh"
+
+using namespace iert;
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+struct DeltaPrepArgs {
+  const void* proj;        // [T, ld] run dtype: q [G*D] | k [G*D] | v [H*V] | ...
+  long long ld;
+  const float* gates;      // [T, gld] fp32: b [H] | a [H]
+  long long gld;
+  const float* conv_w;     // [C, taps] fp32, C = 2*G*D + H*V
+  const float* A_log;      // [H]
+  const float* dt_bias;    // [H]
+  float* state;            // per slot: conv ring [taps, C] at conv_off
+  long long state_stride, conv_off;
+  float* qkv;              // out [T, C] fp32
+  float* beta;             // out [T, H]
+  float* decay;            // out [T, H]
+  int G, D, H, V, taps;
+};
+
+template <typename T>
+__global__ void delta_prep_kernel(DeltaPrepArgs a, IertBatchView b) {
+  extern __shared__ float row[];           // [C]
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int s = sequence_of_token(b, t);
+  const int slot = s >= 0 ? b.slot_ids[s] : -1;
+  if (slot < 0) return;
+  const int GD = a.G * a.D, C = 2 * GD + a.H * a.V, taps = a.taps;
+  const int q_begin = b.cu_q[s], q_end = b.cu_q[s + 1];
+  const int pos = b.pos0[s] + (t - q_begin);
+  const T* proj = (const T*)a.proj;
+  float* ring = a.state + (size_t)slot * a.state_stride + a.conv_off;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = taps - 1; j >= 0; --j) {          // oldest first
+      const int tj = t - j;
+      float x = 0.f;
+      if (tj >= q_begin) x = to_f32(proj[(size_t)tj * a.ld + c]);
+      else if (pos - j >= 0) x = ring[(size_t)((pos - j) % taps) * C + c];
+      acc = fmaf(a.conv_w[(size_t)c * taps + (taps - 1 - j)], x, acc);
+    }
+    row[c] = silu_f(acc);
+    if (t >= q_end - taps)                          // the sequence's newest inputs are its history
+      ring[(size_t)(pos % taps) * C + c] = to_f32(proj[(size_t)t * a.ld + c]);
+  }
+  __syncthreads();
+  // unit vectors: one warp per (q or k, head)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int v = warp; v < 2 * a.G; v += nwarps) {
+    float* x = row + (size_t)v * a.D;
+    float ss = 0.f;
+    for (int d = lane; d < a.D; d += 32) ss = fmaf(x[d], x[d], ss);
+    ss = warp_sum(ss);
+    float f = 1.0f / sqrtf(ss + 1e-6f);
+    if (v < a.G) f *= 1.0f / sqrtf((float)a.D);
+    for (int d = lane; d < a.D; d += 32) x[d] *= f;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) a.qkv[(size_t)t * C + c] = row[c];
+  for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
+    const float gb = a.gates[(size_t)t * a.gld + h], ga = a.gates[(size_t)t * a.gld + a.H + h];
+    a.beta[(size_t)t * a.H + h] = sigmoid_f(gb);
+    a.decay[(size_t)t * a.H + h] = expf(-expf(a.A_log[h]) * softplus_f(ga + a.dt_bias[h]));
+  }
+}
+
+// o [T, H*V] fp32; gate: column gate_off + h*V + e of the packed projection; weight index
+// h*V + e (per_head = 0) or e (per_head = 1: one vector shared by the heads);
+// act 0: SiLU(gate), 1: sigmoid(gate).  One warp per (token, head).
+template <typename T>
+__global__ void gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ proj, long long ld,
+                                       int gate_off, const float* __restrict__ w, int per_head, int act,
+                                       float eps, T* __restrict__ out, int n_tokens, int H, int V) {
+  pdl_wait();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= n_tokens * H) return;
+  const int t = warp / H, h = warp - t * H;
+  const float* x = o + ((size_t)t * H + h) * V;
+  float ss = 0.f;
+  for (int e = lane; e < V; e += 32) ss = fmaf(x[e], x[e], ss);
+  const float r = 1.0f / sqrtf(warp_sum(ss) / (float)V + eps);
+  const T* g = proj + (size_t)t * ld + gate_off + (size_t)h * V;
+  T* y = out + ((size_t)t * H + h) * V;
+  for (int e = lane; e < V; e += 32) {
+    const float gv = to_f32(g[e]);
+    const float ga = act == 0 ? silu_f(gv) : sigmoid_f(gv);
+    y[e] = from_f32<T>(x[e] * r * w[per_head ? e : h * V + e] * ga);
+  }
+}
+
+}  // namespace
+
+IERT_API int iert_delta_prep(const void* proj, int dtype, long long ld, const float* gates, long long gld,
+                             const float* conv_w, const float* A_log, const float* dt_bias, float* state,
+                             long long state_stride, long long conv_off, float* qkv, float* beta, float* decay,
+                             int G, int D, int H, int V, int taps, const IertBatchView* batch, cudaStream_t stream) {
+  if (batch->n_tokens <= 0) return IERT_OK;
+  const long long C = 2LL * G * D + (long long)H * V;
+  if (G <= 0 || D <= 0 || H <= 0 || V <= 0 || taps <= 0 || C > 11000) return IERT_BAD_ARGUMENT;
+  DeltaPrepArgs a = {proj, ld, gates, gld, conv_w, A_log, dt_bias, state, state_stride, conv_off, qkv, beta, decay,
+                     G, D, H, V, taps};
+  const size_t smem = (size_t)C * sizeof(float);
+  if (dtype == IERT_F32) launch_dep(delta_prep_kernel<float>, dim3(batch->n_tokens), dim3(256), smem, stream, a, *batch);
+  else if (dtype == IERT_BF16) launch_dep(delta_prep_kernel<__nv_bfloat16>, dim3(batch->n_tokens), dim3(256), smem, stream, a, *batch);
+  else return IERT_BAD_ARGUMENT;
+  return iert_check_launch("delta_prep");
+}
+
+IERT_API int iert_gated_head_norm(const float* o, const void* proj, int dtype, long long ld, int gate_off,
+                                  const float* w, int per_head, int act, float eps, void* out, int n_tokens,
+                                  int H, int V, cudaStream_t stream) {
+  if (n_tokens <= 0) return IERT_OK;
+  if (H <= 0 || V <= 0) return IERT_BAD_ARGUMENT;
+  const long long warps = (long long)n_tokens * H;
+  const unsigned blocks = (unsigned)((warps + 3) / 4);
+  if (dtype == IERT_F32)
+    launch_dep(gated_head_norm_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, (const float*)proj, ld, gate_off, w,
+               per_head, act, eps, (float*)out, n_tokens, H, V);
+  else if (dtype == IERT_BF16)
+    launch_dep(gated_head_norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, (const __nv_bfloat16*)proj,
+               ld, gate_off, w, per_head, act, eps, (__nv_bfloat16*)out, n_tokens, H, V);
+  else return IERT_BAD_ARGUMENT;
+  return iert_check_launch("gated_head_norm");
+}

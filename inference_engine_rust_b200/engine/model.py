@@ -45,32 +45,49 @@ class Model:
         self.lm_head = part_class("head", spec.head.kind)(spec.head, h, spec.vocab_size, rt)
         self.inputs = [(part_class("input", ps.kind)(ps, h, spec.vocab_size, rt), prefix) for ps, prefix in spec.inputs]
         self.loaded = False
+        # called after every scheduled layer with (its position, the residual rows or streams, the step's
+        # context): for looking at the residual between layers; runs inside the step, so it must launch on
+        # the step's stream and turns captured graphs off for as long as it is set
+        self.after_block = None
         self.ignored_tensors: List[str] = []
         self.notes: List[str] = []       # what loading decided on its own (tied head, ignored tensors)
 
     # ---- weights ------------------------------------------------------------------------
+    @staticmethod
+    def _norm_names(norm, weight_name: str) -> Dict[str, str]:
+        """Tensor name of each of a norm's tensors: its "weight" under the name the spec gives, any
+        other (a bias "b", say) under that name + "." + its local name."""
+        return {local: weight_name if local == "weight" else f"{weight_name}.{local}" for local in norm.tensor_specs()}
+
+    def _norm_specs(self, norm, weight_name: str) -> Dict[str, TensorSpec]:
+        specs = norm.tensor_specs()
+        return {name: specs[local] for local, name in self._norm_names(norm, weight_name).items()}
+
     def expected_tensors(self) -> Dict[str, TensorSpec]:
         """Every tensor name the model reads from a folder, with its shape."""
         spec = self.spec
         out: Dict[str, TensorSpec] = {
             spec.embedding_name: TensorSpec((spec.vocab_size, spec.hidden_size)),
-            spec.final_norm_name: self.final_norm.tensor_specs()["weight"],
         }
+        out.update(self._norm_specs(self.final_norm, spec.final_norm_name))
         if spec.lm_head_name is not None:
             out[spec.lm_head_name] = self.lm_head.tensor_specs()["weight"]
         for part, prefix in self.inputs:
             for local, ts in part.tensor_specs().items():
                 out[prefix + local] = ts
-        for ls, (norm1, mixer, norm2, ffn), extra in zip(spec.layers, self._layer_parts, self._extra_norms):
-            out[ls.mixer_norm_name] = norm1.tensor_specs()["weight"]
+        for ls, (norm1, mixer, norm2, ffn), extra, block in zip(spec.layers, self._layer_parts, self._extra_norms,
+                                                                self.blocks):
+            out.update(self._norm_specs(norm1, ls.mixer_norm_name))
             for local, ts in mixer.tensor_specs().items():
                 out[ls.mixer_prefix + local] = ts
             if ffn is not None:
-                out[ls.ffn_norm_name] = norm2.tensor_specs()["weight"]
+                out.update(self._norm_specs(norm2, ls.ffn_norm_name))
                 for local, ts in ffn.tensor_specs().items():
                     out[ls.ffn_prefix + local] = ts
             for role, norm in extra.items():
-                out[ls.extra_norms[role][1]] = norm.tensor_specs()["weight"]
+                out.update(self._norm_specs(norm, ls.extra_norms[role][1]))
+            for local, ts in block.tensor_specs().items():        # an arrangement with tensors of its own
+                out[ls.block_prefix + local] = ts
         return out
 
     def load(self, source, where: str = "weights", strict: bool = True) -> None:
@@ -103,8 +120,11 @@ class Model:
         def get(name):
             return tensors.pop(name)
 
+        def load_norm(norm, weight_name):
+            norm.load({local: get(name) for local, name in self._norm_names(norm, weight_name).items()})
+
         self.embedding = get(spec.embedding_name)
-        self.final_norm.load({"weight": get(spec.final_norm_name)})
+        load_norm(self.final_norm, spec.final_norm_name)
         self.lm_head.load({"weight": self.embedding if head_name is None else get(head_name)})
         tied = getattr(self.lm_head, "weight", None)
         if head_name is None and tied is not None and tied.dtype == self.embedding.dtype \
@@ -112,14 +132,17 @@ class Model:
             self.embedding = tied                          # tied: one copy
         for part, prefix in self.inputs:
             part.load({local: get(prefix + local) for local in part.tensor_specs()})
-        for ls, (norm1, mixer, norm2, ffn), extra in zip(spec.layers, self._layer_parts, self._extra_norms):
-            norm1.load({"weight": get(ls.mixer_norm_name)})
+        for ls, (norm1, mixer, norm2, ffn), extra, block in zip(spec.layers, self._layer_parts, self._extra_norms,
+                                                                self.blocks):
+            load_norm(norm1, ls.mixer_norm_name)
             mixer.load({local: get(ls.mixer_prefix + local) for local in mixer.tensor_specs()})
             if ffn is not None:
-                norm2.load({"weight": get(ls.ffn_norm_name)})
+                load_norm(norm2, ls.ffn_norm_name)
                 ffn.load({local: get(ls.ffn_prefix + local) for local in ffn.tensor_specs()})
             for role, norm in extra.items():
-                norm.load({"weight": get(ls.extra_norms[role][1])})
+                load_norm(norm, ls.extra_norms[role][1])
+            if block.tensor_specs():
+                block.load({local: get(ls.block_prefix + local) for local in block.tensor_specs()})
         self.loaded = True
 
     def load_random(self, seed: int, std: float = 0.02, on_device: bool = False) -> None:
@@ -146,7 +169,7 @@ class Model:
             parts.extend(p for p in self._layer_parts[e.layer] if p is not None)
             parts.extend(self._extra_norms[e.layer].values())
             parts.append(self.blocks[e.layer])
-        return all(getattr(p, "graph_safe", False) for p in parts)
+        return self.after_block is None and all(getattr(p, "graph_safe", False) for p in parts)
 
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights a one-token step reads: every matrix each scheduled layer uses,
@@ -203,15 +226,26 @@ class Model:
         ctx.rows_ahead = finish() if finish is not None else None
         for part, _ in self.inputs:
             part.prepare(tokens, x, ctx)
+        S = spec.residual_streams
+        rows = x
+        if S is not None:
+            # the residual as S streams per token, all equal to the embedded row at the start
+            rows = ws.take("model.streams", (T, S, H), torch.float32)
+            B.streams_expand(x, rows, T, S, H, ctx.stream)
         for pos, e in enumerate(sched):
             view = cache.layer_view(spec.cache_entry(pos))
             ctx.next_block = self.blocks[sched[pos + 1].layer] if pos + 1 < len(sched) else None
-            self.blocks[e.layer].forward(x, ctx, view, e.writes_cache)
+            self.blocks[e.layer].forward(rows, ctx, view, e.writes_cache)
+            if self.after_block is not None:
+                self.after_block(pos, rows, ctx)
         ctx.rows_ahead = None
         if n_logit_rows == 0:
             return None
         hn = ws.take("model.head_in", (n_logit_rows, H), rt.dtype)
-        self.final_norm.forward(x, hn, ctx, rows_idx=logit_rows, rows=n_logit_rows)
+        if S is not None:                        # the final norm of the sum of the streams
+            self.final_norm.forward_streams(rows, S, hn, ctx, rows_idx=logit_rows, rows=n_logit_rows)
+        else:
+            self.final_norm.forward(x, hn, ctx, rows_idx=logit_rows, rows=n_logit_rows)
         if logits_out is None:
             logits_out = torch.empty((n_logit_rows, spec.vocab_size), dtype=torch.float32, device=rt.device)
         self.lm_head.forward(hn, logits_out, n_logit_rows, ctx)

@@ -1,10 +1,12 @@
 """The parts layers are assembled from.  Importing this package registers the built-in
 kinds: norm "rmsnorm", position "rope", mixer "attention", ffn "swiglu", block "prenorm",
-head "linear"."""
+head "linear"; norm "layernorm", block "hyper" (a residual of several streams), input "embed_norm",
+head "softcap", ffn "moe", mixers "mlstm", "gated_delta" and "latent_attention"."""
 from .base import (Block, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, Runtime, StepContext, StepInput,
                    Workspace, part_class, register_part, unregister_part)
 from .linear import Linear
-from . import norm, rope, attention, swiglu, block, head  # noqa: F401  (registration)
+from . import (norm, rope, attention, swiglu, block, head, inputs, moe, recurrent,  # noqa: F401  (registration)
+               latent_attention)
 
 __all__ = ["Block", "FeedForward", "Head", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime",
            "StepContext", "StepInput", "Workspace", "part_class", "register_part", "unregister_part", "Linear"]

@@ -4,6 +4,12 @@ half left out for a layer without a feed-forward)
 src/layers/attention.rs:757-759, src/layers/ffn.rs:113-116)."""
 from __future__ import annotations
 
+from typing import Dict, Mapping
+
+import torch
+
+from ..csrc import bindings as B
+from ..weights.loader import TensorSpec
 from .base import Block, Runtime, StepContext, first_norm_request_of, register_part
 
 
@@ -53,4 +59,71 @@ class PreNormBlock(Block):
         return xn
 
 
+class NormedAhead:
+    """Left in `ctx.rows_ahead` by a block that computed the NEXT block's first normed input in the same
+    pass that finished its own update of the streams."""
+
+    def __init__(self, norm, rows, normed):
+        self.norm, self.rows, self.normed = norm, rows, normed
+
+
+class HyperConnectionBlock(Block):
+    """Pre-norm layer over a residual kept as S streams x_1 .. x_S per token.  For sublayer q (1: the
+    mixer, 2: the feed-forward) with learned in[S], out[S] and mix[S, S] (indexed [from, to]):
+
+        u = sum_s in[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix[s, t] x_s + out[t] y   (all t at once)
+
+    Tensors (under the layer's block prefix): hc1.in, hc1.out, hc1.mix and, with a feed-forward, hc2.*.
+    The sublayers add into a zeroed fp32 buffer y; the streams' update after a sublayer and the combination
+    and norm in front of the next one (also the next block's first) are one kernel."""
+    graph_safe = True
+
+    def __init__(self, layer_spec, norm1, mixer, norm2, ffn, rt: Runtime):
+        self.norm1, self.mixer, self.norm2, self.ffn, self.rt = norm1, mixer, norm2, ffn, rt
+        self.streams = int(layer_spec.block["streams"])
+        for n in (norm1, norm2):
+            if n is not None and not hasattr(n, "forward_streams"):
+                raise ValueError(f"block 'hyper' needs a norm with forward_streams, got {type(n).__name__}")
+        self.hc = {}
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        S, out = self.streams, {}
+        for q in ("hc1",) + (("hc2",) if self.ffn is not None else ()):
+            out[q + ".in"] = TensorSpec((S,), "ones_plus_normal")
+            out[q + ".out"] = TensorSpec((S,), "ones_plus_normal")
+            out[q + ".mix"] = TensorSpec((S, S))
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.hc = {k: t.to(torch.float32).contiguous() for k, t in tensors.items()}
+
+    def forward(self, xs, ctx: StepContext, cache_view, writes_cache: bool) -> None:
+        rt, S, T = self.rt, self.streams, ctx.n_tokens
+        H = xs.shape[-1]
+        hc = self.hc
+        ctx.norm_ahead = None
+        y = rt.workspace.take("block.sublayer_out", (T, H), torch.float32)
+        ahead, ctx.rows_ahead = ctx.rows_ahead, None
+        if isinstance(ahead, NormedAhead) and ahead.norm is self.norm1 and ahead.rows is xs:
+            xn = ahead.normed                       # the block before left it (and cleared y)
+        else:
+            xn = rt.workspace.take("block.normed", (T, H), rt.dtype)
+            self.norm1.forward_streams(xs, S, xn, ctx, T, in_coef=hc["hc1.in"], clear=y)
+        self.mixer.forward(xn, y, ctx, cache_view, writes_cache)
+        last = "hc1"
+        if self.ffn is not None:
+            self.norm2.forward_streams(xs, S, xn, ctx, T, in_coef=hc["hc2.in"], update=(y, hc["hc1.mix"], hc["hc1.out"]),
+                                       clear=y)
+            self.ffn.forward(xn, y, ctx)
+            last = "hc2"
+        nxt = ctx.next_block
+        update = (y, hc[last + ".mix"], hc[last + ".out"])
+        if isinstance(nxt, HyperConnectionBlock) and nxt.streams == S:
+            nxt.norm1.forward_streams(xs, S, xn, ctx, T, in_coef=nxt.hc["hc1.in"], update=update, clear=y)
+            ctx.rows_ahead = NormedAhead(nxt.norm1, xs, xn)
+        else:
+            B.streams_norm(xs, S, H, T, ctx.stream, y=y, mix=update[1], outc=update[2], update=True, write_back=True)
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "hyper", HyperConnectionBlock)

@@ -41,4 +41,18 @@ class LinearHead(Head):
         self.proj.apply(hn, logits, n_rows, ctx.stream)
 
 
+class SoftCapHead(LinearHead):
+    """logits <- cap * tanh(logits / cap) after the product (spec: "cap")."""
+
+    def __init__(self, spec: PartSpec, hidden_size: int, vocab_size: int, rt: Runtime):
+        super().__init__(spec, hidden_size, vocab_size, rt)
+        self.cap = float(spec["cap"])
+
+    def forward(self, hn, logits, n_rows: int, ctx: StepContext) -> None:
+        from ..csrc import bindings as B
+        super().forward(hn, logits, n_rows, ctx)
+        B.softcap(logits[:n_rows], self.cap, ctx.stream)
+
+
 register_part("head", "linear", LinearHead)
+register_part("head", "softcap", SoftCapHead)

@@ -1,0 +1,86 @@
+"""Mixture-of-experts feed-forward: `experts` small gated feed-forwards W_down (silu(W_gate h) * (W_up h)),
+of which each token uses the `top` with the largest router logits z = W_r h + b (fp32), weighted by the
+softmax over the chosen logits only; plus, optionally, a shared expert of the same form that every
+token uses with weight 1.
+
+Run as two products over all experts at once: the experts' gate and up matrices are stacked into one
+[gate; up] matrix and their down matrices side by side, so that the activation row of a token is
+[expert 0 | expert 1 | ... | shared]; the block of an expert the token did not choose is multiplied by
+0 (by its routing weight otherwise) before the down product, which then sums exactly the chosen experts'
+outputs and the shared one and adds them to the residual.  The products are the same projection kernels
+the dense feed-forward uses, the step stays free of host decisions (CUDA graphs), and the result does
+not depend on what else is in the batch; the price is that every expert's product is computed for every
+token.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping
+
+import torch
+
+from ..csrc import bindings as B
+from ..weights.loader import TensorSpec
+from .base import FeedForward, Runtime, StepContext, register_part
+from .linear import Linear
+
+
+class MoE(FeedForward):
+    graph_safe = True
+
+    def __init__(self, spec, rt: Runtime):
+        self.rt = rt
+        self.hidden_size = int(spec["hidden_size"])
+        self.experts = int(spec["experts"])
+        self.top = int(spec["top"])
+        self.expert_ff = int(spec["expert_ff"])
+        self.shared_ff = int(spec["shared_ff"]) if spec.get("shared_ff") else 0
+        self.inter = self.experts * self.expert_ff + self.shared_ff
+        self.router = self.router_bias = self.gate_up = self.down = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        h, f = self.hidden_size, self.expert_ff
+        out = {"router": TensorSpec((self.experts, h)), "router.b": TensorSpec((self.experts,))}
+        for e in range(self.experts):
+            out[f"e{e}.gate"] = TensorSpec((f, h))
+            out[f"e{e}.up"] = TensorSpec((f, h))
+            out[f"e{e}.down"] = TensorSpec((h, f))
+        if self.shared_ff:
+            out["shared.gate"] = TensorSpec((self.shared_ff, h))
+            out["shared.up"] = TensorSpec((self.shared_ff, h))
+            out["shared.down"] = TensorSpec((h, self.shared_ff))
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        dt = self.rt.dtype
+        names = [f"e{e}" for e in range(self.experts)] + (["shared"] if self.shared_ff else [])
+        gate_up = torch.cat([tensors[f"{n}.gate"].to(dt) for n in names] + [tensors[f"{n}.up"].to(dt) for n in names], dim=0)
+        self.gate_up = Linear(gate_up, self.rt)
+        self.down = Linear(torch.cat([tensors[f"{n}.down"].to(dt) for n in names], dim=1), self.rt)
+        self.router = Linear(tensors["router"], self.rt)
+        self.router_bias = tensors["router.b"].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.gate_up.nbytes() + self.down.nbytes() + self.router.nbytes()
+
+    def forward(self, xn, residual, ctx: StepContext) -> None:
+        rt, ws, T, I, E = self.rt, self.rt.workspace, ctx.n_tokens, self.inter, self.experts
+        z = ws.take("moe.logits", (T, E), torch.float32)
+        self.router.apply(xn, z, T, ctx.stream)
+        wt = ws.take("moe.weights", (T, E), torch.float32)
+        idx = ws.take("moe.chosen", (T, self.top), torch.int32)
+        w = ws.take("moe.chosen_weights", (T, self.top), torch.float32)
+        B.router_topk(z, self.router_bias, T, E, self.top, wt, idx, w, ctx.stream)
+        act = ws.take("ffn.act", (T, I), rt.dtype)
+        done = False
+        if rt.fast:
+            from . import fast_linear
+            done = fast_linear.apply_gated(self.gate_up, xn, act, T, ctx.stream)
+        if not done:
+            gu = ws.take("ffn.gate_up", (T, 2 * I), rt.dtype)
+            self.gate_up.apply(xn, gu, T, ctx.stream)
+            B.silu_mul(gu, act, T, I, ctx.stream)
+        B.moe_scale(act, wt, T, E, self.expert_ff, ctx.stream)
+        self.down.apply(act, residual, T, ctx.stream, add_residual=True)
+
+
+register_part("ffn", "moe", MoE)

@@ -64,4 +64,43 @@ class RMSNorm(Norm):
         return NormRequest(self, self.weight, self.eps)
 
 
+class LayerNorm(Norm):
+    """out = (x - mean) / sqrt(var + eps) * weight + b, var = mean((x - mean)^2), statistics in fp32.
+    Tensors: "weight" and the bias "b" (found at the weight's name + ".b").
+
+    `forward_streams` is the same norm for a residual kept as S streams per token (hyper-connections):
+    one kernel updates the streams with the output `y` of the sublayer before (x'_t = sum_s mix[s, t] x_s
+    + outc[t] y), clears y for the sublayer to come, combines u = sum_s in_coef[s] x'_s and norms u."""
+    graph_safe = True
+
+    def __init__(self, spec, hidden_size: int, rt: Runtime):
+        self.eps = float(spec["eps"])
+        self.hidden_size = hidden_size
+        self.rt = rt
+        self.weight = None
+        self.bias = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {"weight": TensorSpec((self.hidden_size,), "ones_plus_normal"), "b": TensorSpec((self.hidden_size,))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.bias = tensors["b"].to(torch.float32).contiguous()
+
+    def forward(self, x, out, ctx, rows_idx=None, rows=None) -> None:
+        n = rows if rows is not None else (rows_idx.numel() if rows_idx is not None else x.shape[0])
+        B.streams_norm(x, 1, self.hidden_size, n, ctx.stream, w=self.weight, b=self.bias, eps=self.eps, out=out,
+                       rows_idx=rows_idx)
+
+    def forward_streams(self, xs, n_streams: int, out, ctx, rows: int, rows_idx=None, in_coef=None, update=None,
+                        clear=None) -> None:
+        """`update` = (y, mix [S, S] indexed [from, to], outc [S]): apply and store the streams' update first;
+        `clear`: a [tokens, hidden] fp32 buffer whose rows are zeroed (the next sublayer adds into it)."""
+        y, mix, outc = update if update is not None else (clear, None, None)
+        B.streams_norm(xs, n_streams, self.hidden_size, rows, ctx.stream, y=y, mix=mix, outc=outc,
+                       update=update is not None, write_back=update is not None, zero_y=clear is not None,
+                       in_coef=in_coef, w=self.weight, b=self.bias, eps=self.eps, out=out, rows_idx=rows_idx)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)
