@@ -444,8 +444,17 @@ def main() -> int:
     ap.add_argument("--kernels", action="store_true",
                     help="also time the dominant kernels one by one with CUDA events (projections and decode "
                          "attention at the decode batch, projections at the prefill length): key 'kernels'")
+    ap.add_argument("--design", default=None, choices=["vefulix"],
+                    help="instead of the default workload: prefill and decode of that design at Mistral 7B's width, "
+                         "depth (--layers, default 8) and feed-forward size beside Mistral 7B itself, with a table of "
+                         "each step's kernels against what their bytes and FLOPs allow (one JSON line)")
     a = ap.parse_args()
 
+    if a.design is not None and a.impl != "reference":
+        from inference_engine_rust_b200 import bench_designs
+        print(json.dumps(bench_designs.compare(f"{a.design}-7b-sizes", "7b-v0.1", a.layers or 8, peaks(), a.batch, a.context,
+                                               a.prefill_tokens, min(a.steps, 32), max(3, min(a.warmup, 4)))))
+        return 0
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a Rust crate (no setup.py/pyproject; no cargo or rustc on this image), "

@@ -32,6 +32,29 @@ PRESETS: Dict[str, dict] = {
 }
 
 
+
+def _vefulix(width, vocab, layers, streams, heads, dim, vdim, q_rank, kv_rank, experts, top, expert_ff, shared_ff):
+    """A Vefulix configuration whose layers go round delta, latent attention, mLSTM, latent attention."""
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff}}
+    mixers = [
+        ("delta", {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": vdim, "conv": 4}),
+        ("latent_attention", {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+                              "scale": dim ** -0.5}),
+        ("mlstm", {"heads": max(1, heads // 2), "dim": dim, "vdim": 2 * vdim, "gate_cap": 15.0}),
+        ("latent_attention", {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+                              "scale": dim ** -0.5}),
+    ]
+    return {"architecture": "Vefulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "streams": streams,
+            "logit_softcap": 30.0,
+            "layers": [{"type": mixers[i % 4][0], "mixer": dict(mixers[i % 4][1]), "mlp": dict(moe)} for i in range(layers)]}
+
+
+# Vefulix at the width, head count and total feed-forward size (16 experts of 768 + a shared 2,048 = 14,336)
+# of Mistral 7B, and a tiny one that runs anywhere in seconds.
+PRESETS["vefulix-7b-sizes"] = _vefulix(4096, 32000, 32, 2, 32, 128, 128, 1536, 512, 16, 2, 768, 2048)
+PRESETS["vefulix-tiny"] = _vefulix(96, 320, 4, 2, 4, 16, 24, 48, 40, 6, 2, 32, 64)
+
+
 def preset(name: str) -> dict:
     """A copy of the named configuration (a config.json-style dict)."""
     try:

@@ -79,7 +79,8 @@ __device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* sr
 
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out,
-                         IertBatchView b, int heads, int kv_heads, int window, float scale_log2e) {
+                         IertBatchView b, int heads, int kv_heads, int window, float scale_log2e,
+                         const float* __restrict__ sink) {
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* q_tile = smem;
   auto k_tile = [&](int i) { return smem + Q_TILE_BYTES + i * TILE_BYTES; };
@@ -218,6 +219,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
   for (int r = 0; r < 2; ++r) {
     l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
     l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
+    // a sink: one more term exp(sink) in the denominator, with no key and no value
+    if (sink && m_row[r] != -INFINITY) l_row[r] += fast_exp2(sink[head] * 1.4426950408889634f - m_row[r]);
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -239,7 +242,7 @@ IERT_API int iert_attention_prefill_head_dim() { return HD; }
 // out: bf16 [T, heads * HEAD_DIM].  Every sequence of the step starts at position 0.
 // max_q_len: the longest sequence of the step (sizes the grid).
 IERT_API int iert_attention_prefill(const void* qkv, void* out, const IertBatchView* batch, int heads,
-                                    int kv_heads, int window, float scale, int max_q_len,
+                                    int kv_heads, int window, float scale, int max_q_len, const float* sink,
                                     cudaStream_t stream) {
   if (batch->n_tokens <= 0 || max_q_len <= 0) return IERT_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || batch->n_seqs > 65535)
@@ -256,7 +259,7 @@ IERT_API int iert_attention_prefill(const void* qkv, void* out, const IertBatchV
   dim3 grid((max_q_len + BM - 1) / BM, heads, batch->n_seqs);
   attention_prefill_kernel<<<grid, THREADS, smem, stream>>>(
       (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, *batch, heads, kv_heads, window,
-      scale * 1.4426950408889634f);
+      scale * 1.4426950408889634f, sink);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
 }

@@ -55,6 +55,7 @@ struct PrefillTcParams {
   __nv_bfloat16* out;         // [T, heads * HD]
   int heads, kv_heads, window;
   float scale_log2e;
+  const float* sink;       // optional [heads]: one more term exp(sink) in every row's denominator (no key, no value)
   int* err;
 };
 
@@ -322,6 +323,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok && !wait_bar(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag)) ok = false;
     if (ok) {
       tc_fence_after();
+      if (p.sink && m_used != -INFINITY) l += ex2(p.sink[head] * 1.4426950408889634f - m_used);
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       __nv_bfloat16* dst = p.out + ((long long)(q_begin + i) * p.heads + head) * HD;
 #pragma unroll
@@ -359,7 +361,7 @@ IERT_API int iert_attention_prefill_tc_available() { return 1; }
 // IERT_BAD_ARGUMENT (nothing launched) when the tensor map cannot be made.
 IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBatchView* batch, int heads,
                                        int kv_heads, int window, float scale, int max_q_len, int* err,
-                                       cudaStream_t stream) {
+                                       const float* sink, cudaStream_t stream) {
   if (batch->n_tokens <= 0 || max_q_len <= 0) return IERT_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || (max_q_len + BM - 1) / BM > 65535 || batch->n_seqs > 65535 ||
       ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15))
@@ -373,6 +375,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
   p.out = (__nv_bfloat16*)out;
   p.heads = heads; p.kv_heads = kv_heads; p.window = window;
   p.scale_log2e = scale * 1.4426950408889634f;
+  p.sink = sink;
   p.err = err;
   const size_t smem = (size_t)NSUB * SUB_BYTES + 4 * (size_t)NSUB * KV_SUB_BYTES + 256;
   static bool configured = false;
@@ -391,7 +394,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
 #else   // other head sizes: the mma.sync kernel serves them
 
 IERT_API int iert_attention_prefill_tc_available() { return 0; }
-IERT_API int iert_attention_prefill_tc(const void*, void*, const IertBatchView*, int, int, int, float, int, int*,
+IERT_API int iert_attention_prefill_tc(const void*, void*, const IertBatchView*, int, int, int, float, int, int*, const float*,
                                        cudaStream_t) {
   return IERT_BAD_ARGUMENT;
 }

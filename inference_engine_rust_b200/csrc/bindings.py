@@ -118,6 +118,7 @@ def _declare(lib) -> None:
         "iert_latent_attention_prompt": [P, LL, P, c_int, POINTER(BatchView), c_int, c_int, c_int, c_float, P, S],
         "iert_latent_attention_decode": [P, LL, P, P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_int, c_int,
                                          c_float, P, P, S],
+        "iert_latent_decode_tc_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
         "iert_router_topk": [P, LL, P, c_int, c_int, c_int, P, P, P, S],
         "iert_moe_scale": [P, c_int, LL, P, c_int, c_int, c_int, S],
     })
@@ -416,7 +417,7 @@ def _attention_lib(head_dim: int):
     if lib is None:
         lib = build.load_library(*build.attention_library(head_dim))
         lib.iert_attention_prefill.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
-                                               c_float, c_int, c_void_p]
+                                               c_float, c_int, c_void_p, c_void_p]
         lib.iert_attention_prefill.restype = c_int
         lib.iert_attention_decode_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
                                                  c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]
@@ -426,7 +427,7 @@ def _attention_lib(head_dim: int):
                                                       c_void_p, c_void_p]
         lib.iert_attention_decode_tc_rope.restype = c_int
         lib.iert_attention_prefill_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
-                                                  c_float, c_int, c_void_p, c_void_p]
+                                                  c_float, c_int, c_void_p, c_void_p, c_void_p]
         lib.iert_attention_prefill_tc.restype = c_int
         lib.iert_attention_prefill_tc_available.restype = c_int
         lib.iert_attention_decode_tc_ctas_per_sm.restype = c_int
@@ -437,11 +438,12 @@ def _attention_lib(head_dim: int):
 
 
 def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, head_dim: int, window: int,
-                      scale: float, max_q_len: int, stream, err=None, legacy: bool = False) -> bool:
+                      scale: float, max_q_len: int, stream, err=None, legacy: bool = False, sink=None) -> bool:
     """Flash prompt attention (bf16) over the step's own keys and values.  Head sizes 64 and
     128 run on tcgen05 with the scores and the output in tensor memory (unless `legacy`); other
     multiples of 16 up to 256 run the mma.sync kernel.  The library is compiled per head size
-    the first time it is needed; anything else returns False and nothing is launched."""
+    the first time it is needed; anything else returns False and nothing is launched.  `sink` (fp32
+    [heads], optional): one more term exp(sink) in each row's softmax denominator."""
     if head_dim % 16 or not 16 <= head_dim <= 256:
         return False
     lib = _attention_lib(head_dim)
@@ -449,14 +451,15 @@ def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, hea
     if not legacy and err is not None and lib.iert_attention_prefill_tc_available() \
             and os.environ.get("IERT_ATTN_TC", "1") != "0":
         status = lib.iert_attention_prefill_tc(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
-                                               window, scale, max_q_len, err.data_ptr(), stream)
+                                               window, scale, max_q_len, err.data_ptr(),
+                                               sink.data_ptr() if sink is not None else None, stream)
         if status == 0:
             launch_count += 1
             return True
         if status != 1:
             raise KernelError("attention_prefill_tc: the launch failed")
     status = lib.iert_attention_prefill(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
-                                        window, scale, max_q_len, stream)
+                                        window, scale, max_q_len, sink.data_ptr() if sink is not None else None, stream)
     if status == 1:
         return False
     if status != 0:
@@ -645,6 +648,36 @@ def latent_attention_decode(q, w_uk, w_uv, out, batch: BatchView, kv: KvView, H:
     check(core().iert_latent_attention_decode(q.data_ptr(), q.stride(0), w_uk.data_ptr(), w_uv.data_ptr(), out.data_ptr(),
                                               dtype_code(q.dtype), byref(batch), byref(kv), H, D, V, scale, _ptr(sink),
                                               err.data_ptr(), stream), "latent_attention_decode")
+
+
+def latent_decode_tc_plan(n_seqs: int, H: int, table_width: int):
+    """(heads padded to whole MMA tiles, runs a sequence is cut into) of the tensor-core one-token kernel."""
+    hpad, splits = c_int(0), c_int(0)
+    core().iert_latent_decode_tc_plan(n_seqs, H, table_width, byref(hpad), byref(splits))
+    return hpad.value, splits.value
+
+
+def latent_attention_decode_tc(q, w_uk, w_uv, out, batch: BatchView, kv: KvView, H: int, D: int, V: int, scale: float, sink,
+                               hpad: int, splits: int, qa, part_m, part_l, part_acc, err, stream) -> bool:
+    """One-token latent attention on the tensor cores (bf16, rank a multiple of 32 up to 512, pages of 64):
+    the absorbed queries, the split attention over the cached latents, the merge with the sink and W_uv.
+    Returns False, having launched nothing, for sizes it does not take."""
+    lib = core()
+    fn = lib.iert_latent_attention_decode_tc
+    if not getattr(fn, "_declared", False):
+        fn.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int, c_int,
+                       c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+        fn.restype = c_int
+        fn._declared = True
+    status = fn(q.data_ptr(), q.stride(0), w_uk.data_ptr(), w_uv.data_ptr(), out.data_ptr(), byref(batch), byref(kv), H, D, V,
+                scale, _ptr(sink), hpad, splits, qa.data_ptr(), part_m.data_ptr(), part_l.data_ptr(), part_acc.data_ptr(),
+                err.data_ptr(), stream)
+    if status == 1:
+        return False
+    check(status, "latent_attention_decode_tc")
+    global launch_count
+    launch_count += 2
+    return True
 
 
 def router_topk(z, bias, n_tokens: int, E: int, top: int, wt, idx, w, stream) -> None:

@@ -91,7 +91,7 @@ class HyperConnectionBlock(Block):
         for q in ("hc1",) + (("hc2",) if self.ffn is not None else ()):
             out[q + ".in"] = TensorSpec((S,), "ones_plus_normal")
             out[q + ".out"] = TensorSpec((S,), "ones_plus_normal")
-            out[q + ".mix"] = TensorSpec((S, S))
+            out[q + ".mix"] = TensorSpec((S, S), "eye_plus_normal")
         return out
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:

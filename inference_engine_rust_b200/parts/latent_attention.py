@@ -73,12 +73,28 @@ class LatentAttention(Mixer):
             qkv = ws.take("latent.qkv", (T, 2 * H * D + H * V), rt.dtype)
             self.uq.apply(cq, qkv[:, :H * D], T, ctx.stream)
             self.ukv.apply(c, qkv[:, H * D:], T, ctx.stream)
-            B.latent_attention_prompt(qkv, out, ctx.batch, H, D, V, self.scale, self.sink, ctx.stream)
+            # keys and values of one size: the tensor-core prompt attention (tcgen05 at 64 and 128), with
+            # every head its own key/value head and the sink in the denominator
+            if not (rt.fast and qkv.dtype == torch.bfloat16 and D == V and
+                    B.attention_prefill(qkv, out, ctx.batch, H, H, D, 0, self.scale, ctx.max_q_len, ctx.stream,
+                                        err=rt.err, sink=self.sink)):
+                B.latent_attention_prompt(qkv, out, ctx.batch, H, D, V, self.scale, self.sink, ctx.stream)
         else:
             q = ws.take("latent.q", (T, H * D), rt.dtype)
             self.uq.apply(cq, q, T, ctx.stream)
-            B.latent_attention_decode(q, self.w_uk, self.w_uv, out, ctx.batch, kv, H, D, V, self.scale, self.sink,
-                                      rt.err, ctx.stream)
+            done = False
+            if rt.fast and q.dtype == torch.bfloat16 and ctx.kind == "decode":
+                hpad, splits = B.latent_decode_tc_plan(ctx.n_seqs, H, cache_view.group.table_width)
+                rank = self.kv_rank
+                qa = ws.take("latent.qa", (T, hpad, rank), torch.bfloat16)
+                part_m = ws.take("latent.part_m", (T, splits, hpad), torch.float32)
+                part_l = ws.take("latent.part_l", (T, splits, hpad), torch.float32)
+                part_acc = ws.take("latent.part_acc", (T, splits, hpad, rank), torch.float32)
+                done = B.latent_attention_decode_tc(q, self.w_uk, self.w_uv, out, ctx.batch, kv, H, D, V, self.scale,
+                                                    self.sink, hpad, splits, qa, part_m, part_l, part_acc, rt.err, ctx.stream)
+            if not done:
+                B.latent_attention_decode(q, self.w_uk, self.w_uv, out, ctx.batch, kv, H, D, V, self.scale, self.sink,
+                                          rt.err, ctx.stream)
         self.o.apply(out, residual, T, ctx.stream, add_residual=True)
 
 

@@ -23,7 +23,8 @@ from .safetensors_io import TensorSource, write_safetensors
 class TensorSpec:
     """What a part expects under one name.  `init` tells the random-weights mode how to
     fill it: "normal" = N(0, std); "ones_plus_normal" = 1 + N(0, std) (norm scales);
-    "int_table" = integers (kept as int32)."""
+    "eye_plus_normal" = identity + N(0, std) (square mixing matrices); "int_table" = integers
+    (kept as int32)."""
 
     shape: Tuple[int, ...]
     init: str = "normal"
@@ -148,6 +149,8 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, std: float,
     t = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32) * std
     if spec.init == "ones_plus_normal":
         t += 1.0
+    elif spec.init == "eye_plus_normal":
+        t += torch.eye(spec.shape[-1], dtype=torch.float32, device=device)
     elif spec.init != "normal":
         raise ValueError(f"tensor {name!r}: unknown init {spec.init!r}")
     return t.to(dtype)
