@@ -35,10 +35,17 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t lds32(const __nv_bfloat16* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
-template <typename T>
-__global__ void latent_absorb_q_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ w_uk,
-                                       __nv_bfloat16* __restrict__ qa, int H, int Hpad, int D, int rank) {
-  extern __shared__ float q_s[];
+// qa[t, h, :] = sum_d q[t, h, d] W_uk[h*D + d, :].  A block of 256 threads takes one (token, head): 64 threads
+// across the rank (eight columns each, 16-byte loads of the weights) times four groups along d, added
+// through shared memory in a fixed order.
+constexpr int ABSORB_THREADS = 256;
+
+__global__ void __launch_bounds__(ABSORB_THREADS)
+latent_absorb_q_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __nv_bfloat16* __restrict__ w_uk,
+                       __nv_bfloat16* __restrict__ qa, int H, int Hpad, int D, int rank) {
+  extern __shared__ float sm_q[];
+  float* q_s = sm_q;                    // [D]
+  float* part = sm_q + D;               // [4][rank]
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   __nv_bfloat16* dst = qa + ((size_t)t * Hpad + h) * rank;
@@ -46,14 +53,31 @@ __global__ void latent_absorb_q_kernel(const T* __restrict__ q, long long ldq, c
     for (int r = threadIdx.x; r < rank; r += blockDim.x) dst[r] = __float2bfloat16_rn(0.f);
     return;
   }
-  for (int d = threadIdx.x; d < D; d += blockDim.x) q_s[d] = to_f32(q[(size_t)t * ldq + (size_t)h * D + d]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) q_s[d] = __bfloat162float(q[(size_t)t * ldq + (size_t)h * D + d]);
   __syncthreads();
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) {
-    const T* w = w_uk + (size_t)h * D * rank + r;
-    float a = 0.f;
-    for (int d = 0; d < D; ++d) a = fmaf(q_s[d], to_f32(w[(size_t)d * rank]), a);
-    dst[r] = __float2bfloat16_rn(a);
+  const int grp = threadIdx.x >> 6, lane64 = threadIdx.x & 63;
+  const int d_lo = grp * ((D + 3) / 4), d_hi = min(D, d_lo + (D + 3) / 4);
+  for (int r0 = lane64 * 8; r0 < rank; r0 += 64 * 8) {
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const __nv_bfloat16* w = w_uk + (size_t)h * D * rank + r0;
+#pragma unroll 4
+    for (int d = d_lo; d < d_hi; ++d) {
+      const uint4 v = *reinterpret_cast<const uint4*>(w + (size_t)d * rank);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+      const float qd = q_s[d];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p[e]);
+        a[2 * e] = fmaf(qd, f.x, a[2 * e]);
+        a[2 * e + 1] = fmaf(qd, f.y, a[2 * e + 1]);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) part[grp * rank + r0 + e] = a[e];
   }
+  __syncthreads();
+  for (int r = threadIdx.x; r < rank; r += blockDim.x)
+    dst[r] = __float2bfloat16_rn((part[r] + part[rank + r]) + (part[2 * rank + r] + part[3 * rank + r]));
 }
 
 template <int MT>
@@ -74,8 +98,7 @@ latent_decode_tc_kernel(const __nv_bfloat16* __restrict__ qa, IertBatchView b, I
   if (slot < 0) return;
   const int n_keys = b.pos0[s] + 1;                  // one token per sequence: its own row is in the cache
   const int n_tiles = (n_keys + BK - 1) / BK;
-  const int per = (n_tiles + splits - 1) / splits;
-  const int t_lo = split * per, t_hi = min(n_tiles, t_lo + per);
+  const int t_lo = (int)((long long)split * n_tiles / splits), t_hi = (int)((long long)(split + 1) * n_tiles / splits);
   const size_t part_row0 = ((size_t)s * splits + split) * Hpad + rows0;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
   if (t_lo >= t_hi) {                                // an empty run: a partial that the merge skips
@@ -250,32 +273,60 @@ latent_decode_merge_kernel(const float* __restrict__ part_m, const float* __rest
     for (int e = threadIdx.x; e < V; e += THREADS) o[e] = from_f32<T>(0.f);
     return;
   }
-  if (threadIdx.x == 0) {
-    float M = sink ? sink[h] : -INFINITY;
-    for (int i = 0; i < splits; ++i) M = fmaxf(M, part_m[((size_t)t * splits + i) * Hpad + h]);
-    float L = sink ? expf(sink[h] - M) : 0.f;
-    for (int i = 0; i < splits; ++i) {
-      const size_t row = ((size_t)t * splits + i) * Hpad + h;
-      const float w = part_m[row] == -INFINITY ? 0.f : expf(part_m[row] - M);
-      wgt[i] = w;
-      L += w * part_l[row];
+  if (threadIdx.x < 32) {                 // splits <= 64: two runs per lane
+    const int lane = threadIdx.x;
+    float mi[2], li[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = lane + 32 * k;
+      const size_t row = ((size_t)t * splits + (i < splits ? i : 0)) * Hpad + h;
+      mi[k] = i < splits ? part_m[row] : -INFINITY;
+      li[k] = i < splits ? part_l[row] : 0.f;
     }
+    const float snk = sink ? sink[h] : -INFINITY;
+    const float M = fmaxf(warp_max(fmaxf(mi[0], mi[1])), snk);
+    float w[2], part = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      w[k] = mi[k] == -INFINITY ? 0.f : expf(mi[k] - M);
+      part += w[k] * li[k];
+    }
+    const float L = warp_sum(part) + (sink ? expf(snk - M) : 0.f);
     const float inv = L > 0.f ? 1.0f / L : 0.f;
-    for (int i = 0; i < splits; ++i) wgt[i] *= inv;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) if (lane + 32 * k < splits) wgt[lane + 32 * k] = w[k] * inv;
   }
   __syncthreads();
   for (int r = threadIdx.x; r < rank; r += THREADS) {
     float a = 0.f;
-    for (int i = 0; i < splits; ++i)
-      if (wgt[i] != 0.f) a = fmaf(wgt[i], part_acc[(((size_t)t * splits + i) * Hpad + h) * rank + r], a);
+    for (int i0 = 0; i0 < splits; i0 += 4) {          // four runs' loads in flight; an empty run's row is never read
+      float v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = i0 + k;
+        const bool live = i < splits && wgt[i < splits ? i : 0] != 0.f;
+        v[k] = live ? part_acc[(((size_t)t * splits + i) * Hpad + h) * rank + r] : 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) if (i0 + k < splits) a = fmaf(wgt[i0 + k], v[k], a);
+    }
     lat[r] = a;
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int e = warp; e < V; e += THREADS / 32) {
+  for (int e = warp; e < V; e += THREADS / 32) {      // rank is a multiple of 32: 16-byte loads of eight weights
     const T* w = w_uv + ((size_t)h * V + e) * rank;
     float a = 0.f;
-    for (int r = lane; r < rank; r += 32) a = fmaf(to_f32(w[r]), lat[r], a);
+    for (int r = lane * 8; r < rank; r += 32 * 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(w + r);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(p[k]);
+        a = fmaf(f.x, lat[r + 2 * k], a);
+        a = fmaf(f.y, lat[r + 2 * k + 1], a);
+      }
+    }
     a = warp_sum(a);
     if (lane == 0) o[e] = from_f32<T>(a);
   }
@@ -294,7 +345,9 @@ IERT_API int iert_latent_decode_tc_plan(int n_seqs, int H, int table_width, int*
   *Hpad = groups * mt * 16;
   int want = (2 * iert_sm_count_cached() + n_seqs * groups - 1) / (n_seqs * groups > 0 ? n_seqs * groups : 1);
   if (want > 32) want = 32;
-  if (want > table_width) want = table_width;
+  // a run's partial result (heads x rank floats) is as many bytes as 16 or more cached rows: runs of fewer than
+  // four tiles of the longest sequence the cache can hold cost more than they spread
+  if (want > (table_width + 3) / 4) want = (table_width + 3) / 4;
   if (want < 1) want = 1;
   *splits = want;
   return IERT_OK;
@@ -326,7 +379,7 @@ IERT_API int iert_latent_attention_decode_tc(const void* q, long long ldq, const
     }
     configured = true;
   }
-  launch_dep(latent_absorb_q_kernel<__nv_bfloat16>, dim3(T, Hpad), dim3(128), (size_t)D * sizeof(float), stream,
+  launch_dep(latent_absorb_q_kernel, dim3(T, Hpad), dim3(ABSORB_THREADS), (size_t)(D + 4 * rank) * sizeof(float), stream,
              (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)w_uk, (__nv_bfloat16*)qa, H, Hpad, D, rank);
   dim3 grid(T, splits, Hpad / (mt * 16));
   if (mt == 2)

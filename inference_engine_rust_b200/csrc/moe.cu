@@ -59,6 +59,20 @@ __global__ void moe_scale_kernel(T* __restrict__ act, long long ld, const float*
   pdl_wait();
   const int t = blockIdx.x;
   T* row = act + (size_t)t * ld;
+  if (sizeof(T) == 2 && F % 8 == 0 && ld % 8 == 0 && ((uintptr_t)act & 15) == 0) {      // eight at a time
+    for (int i = threadIdx.x * 8; i < E * F; i += blockDim.x * 8) {
+      const float w = wt[(size_t)t * E + i / F];
+      uint4 v = *reinterpret_cast<const uint4*>(row + i);
+      __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p[e]);
+        p[e] = __floats2bfloat162_rn(f.x * w, f.y * w);
+      }
+      *reinterpret_cast<uint4*>(row + i) = v;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < E * F; i += blockDim.x)
     row[i] = from_f32<T>(to_f32(row[i]) * wt[(size_t)t * E + i / F]);
 }

@@ -3,8 +3,13 @@
 //
 // Work split: a column j of S never meets another column, so a CTA owns (sequence, head, a run of
 // columns) and a thread owns RPT = ceil(DIM / R) rows of one column in registers; the R threads of a
-// column are neighbouring lanes and add their partial dot products by shuffles.  A CTA walks its
-// sequence's tokens in order; the tokens' vectors come through shared memory CHUNK tokens at a time.
+// column are neighbouring lanes and add their partial dot products by shuffles.  R is chosen at the
+// launch: the tokens of a sequence are a chain, so all the parallelism there is lies in heads x columns x
+// R, and a single prompt wants many lanes per column (more warps per SM to hide the chain's latency)
+// where a batch of sequences is served best by few (fewer shuffles and shared-memory reads per FMA).
+// A CTA walks its sequence's tokens in order; the tokens' vectors come through shared memory CHUNK
+// tokens at a time, fetched (and converted) by two warps that do nothing else into the buffer the
+// computing warps are not reading, so that those never wait for memory: one barrier per chunk.
 // State is read when the CTA starts and written back when it ends, so a step of one token and a
 // prompt of thousands run the same code.
 //
@@ -22,16 +27,16 @@ using namespace iert;
 
 namespace {
 
-constexpr int lanes_per_column() {
+constexpr int fewest_lanes() {                 // the fewest lanes per column that keep a thread's rows at 32 or fewer
   int r = 1;
   while ((DIM + r - 1) / r > 32 && r < 32) r *= 2;
   return r;
 }
-constexpr int R = lanes_per_column();
-constexpr int RPT = (DIM + R - 1) / R;
-constexpr int CHUNK = 8;
-constexpr int MAX_COLS = 128 / R > 0 ? (256 / R) : 1;      // columns per CTA (threads = cols * R <= 256)
+constexpr int R_MIN = fewest_lanes();
+constexpr int CHUNK = DIM <= 128 ? 8 : DIM <= 256 ? 4 : DIM <= 512 ? 2 : 1;
+constexpr int LOADERS = 64;                    // threads of a CTA that only fetch
 
+template <int R>
 __device__ __forceinline__ float group_sum(float v) {
 #pragma unroll
   for (int o = R / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -48,18 +53,39 @@ struct DeltaArgs {
   int G, H, V, cols;
 };
 
-__global__ void __launch_bounds__(256) delta_recur_kernel(DeltaArgs a, IertBatchView b) {
-  __shared__ float k_s[CHUNK][DIM], q_s[CHUNK][DIM], v_s[CHUNK][256], bg_s[CHUNK][2];
+template <int R>
+__global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a, IertBatchView b) {
+  constexpr int RPT = (DIM + R - 1) / R;
+  __shared__ float k_s[2][CHUNK][DIM], q_s[2][CHUNK][DIM], v_s[2][CHUNK][256], bg_s[2][CHUNK][2];
   pdl_wait();
   const int s = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * a.cols;
   const int slot = b.slot_ids[s];
   const int t0 = b.cu_q[s], t1 = b.cu_q[s + 1];
   if (slot < 0 || t1 <= t0) return;
+  const int workers = blockDim.x - LOADERS;
+  const bool loader = (int)threadIdx.x >= workers;
   const int col = threadIdx.x / R, r = threadIdx.x % R;
   const int j = c0 + col;
-  const bool live = col < a.cols && j < a.V;
+  const bool live = !loader && col < a.cols && j < a.V;
   const int g = head / (a.H / a.G);
   const int GD = a.G * DIM, C = 2 * GD + a.H * a.V;
+  auto fetch = [&](int buf, int tc, int tid, int nthreads) {
+    const int n = min(CHUNK, t1 - tc);
+    for (int x = tid; x < n * DIM; x += nthreads) {
+      const int tt = x / DIM, d = x - tt * DIM;
+      const float* rowp = a.qkv + (size_t)(tc + tt) * C;
+      q_s[buf][tt][d] = rowp[g * DIM + d];
+      k_s[buf][tt][d] = rowp[GD + g * DIM + d];
+    }
+    for (int x = tid; x < n * a.cols; x += nthreads) {
+      const int tt = x / a.cols, cc = x - tt * a.cols;
+      v_s[buf][tt][cc] = c0 + cc < a.V ? a.qkv[(size_t)(tc + tt) * C + 2 * GD + head * a.V + c0 + cc] : 0.f;
+    }
+    if (tid < n) {
+      bg_s[buf][tid][0] = a.beta[(size_t)(tc + tid) * a.H + head];
+      bg_s[buf][tid][1] = a.decay[(size_t)(tc + tid) * a.H + head];
+    }
+  };
   float* Sg = a.state + (size_t)slot * a.state_stride + a.s_off + (size_t)head * DIM * a.V;
   float S[RPT];
 #pragma unroll
@@ -67,47 +93,39 @@ __global__ void __launch_bounds__(256) delta_recur_kernel(DeltaArgs a, IertBatch
     const int d = r * RPT + i;
     S[i] = (live && d < DIM) ? Sg[(size_t)d * a.V + j] : 0.f;
   }
-  for (int tc = t0; tc < t1; tc += CHUNK) {
+  fetch(0, t0, threadIdx.x, blockDim.x);
+  __syncthreads();
+  int buf = 0;
+  for (int tc = t0; tc < t1; tc += CHUNK, buf ^= 1) {
     const int n = min(CHUNK, t1 - tc);
-    __syncthreads();
-    for (int x = threadIdx.x; x < n * DIM; x += blockDim.x) {
-      const int tt = x / DIM, d = x - tt * DIM;
-      const float* rowp = a.qkv + (size_t)(tc + tt) * C;
-      q_s[tt][d] = rowp[g * DIM + d];
-      k_s[tt][d] = rowp[GD + g * DIM + d];
-    }
-    for (int x = threadIdx.x; x < n * a.cols; x += blockDim.x) {
-      const int tt = x / a.cols, cc = x - tt * a.cols;
-      v_s[tt][cc] = c0 + cc < a.V ? a.qkv[(size_t)(tc + tt) * C + 2 * GD + head * a.V + c0 + cc] : 0.f;
-    }
-    if (threadIdx.x < n) {
-      bg_s[threadIdx.x][0] = a.beta[(size_t)(tc + threadIdx.x) * a.H + head];
-      bg_s[threadIdx.x][1] = a.decay[(size_t)(tc + threadIdx.x) * a.H + head];
-    }
-    __syncthreads();
-    for (int tt = 0; tt < n; ++tt) {
-      const float beta = bg_s[tt][0], gd = bg_s[tt][1];
-      float kk[RPT];
-      float dk = 0.f;
+    if (loader) {
+      if (tc + CHUNK < t1) fetch(buf ^ 1, tc + CHUNK, threadIdx.x - workers, LOADERS);
+    } else {
+      for (int tt = 0; tt < n; ++tt) {
+        const float beta = bg_s[buf][tt][0], gd = bg_s[buf][tt][1];
+        float kk[RPT];
+        float dk = 0.f;
 #pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const int d = r * RPT + i;
-        kk[i] = d < DIM ? k_s[tt][d] : 0.f;
-        S[i] *= gd;
-        dk = fmaf(S[i], kk[i], dk);
-      }
-      dk = group_sum(dk);
-      const float u = beta * ((live ? v_s[tt][col] : 0.f) - dk);
-      float oq = 0.f;
+        for (int i = 0; i < RPT; ++i) {
+          const int d = r * RPT + i;
+          kk[i] = d < DIM ? k_s[buf][tt][d] : 0.f;
+          S[i] *= gd;
+          dk = fmaf(S[i], kk[i], dk);
+        }
+        dk = group_sum<R>(dk);
+        const float u = beta * ((live ? v_s[buf][tt][col] : 0.f) - dk);
+        float oq = 0.f;
 #pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const int d = r * RPT + i;
-        S[i] = fmaf(kk[i], u, S[i]);
-        oq = fmaf(S[i], d < DIM ? q_s[tt][d] : 0.f, oq);
+        for (int i = 0; i < RPT; ++i) {
+          const int d = r * RPT + i;
+          S[i] = fmaf(kk[i], u, S[i]);
+          oq = fmaf(S[i], d < DIM ? q_s[buf][tt][d] : 0.f, oq);
+        }
+        oq = group_sum<R>(oq);
+        if (live && r == 0) a.o[(size_t)(tc + tt) * a.H * a.V + (size_t)head * a.V + j] = oq;
       }
-      oq = group_sum(oq);
-      if (live && r == 0) a.o[(size_t)(tc + tt) * a.H * a.V + (size_t)head * a.V + j] = oq;
     }
+    __syncthreads();
   }
   if (live) {
 #pragma unroll
@@ -137,54 +155,64 @@ __device__ __forceinline__ float logsigmoid_f(float x) { return fminf(x, 0.f) - 
 
 // The part of the recurrence that no column of S takes part in: the gates, the running maximum m,
 // the normaliser n and the read-out's denominator.  One warp per (sequence, head) walks the tokens
-// and leaves three numbers per token for the CTAs that own the columns.
+// and leaves three numbers per token for the CTAs that own the columns; three more warps fetch the
+// next tokens' q and k meanwhile and work out their gates' logarithms, which need no earlier token.
 constexpr int NPL = (DIM + 31) / 32;          // entries of n per lane
+constexpr int SCHUNK = DIM <= 64 ? 32 : DIM <= 128 ? 16 : DIM <= 256 ? 8 : DIM <= 512 ? 4 : 2;
 
 template <typename T>
-__global__ void __launch_bounds__(32) mlstm_scan_kernel(MlstmArgs a, IertBatchView b) {
+__global__ void __launch_bounds__(128) mlstm_scan_kernel(MlstmArgs a, IertBatchView b) {
+  __shared__ float k_s[2][SCHUNK][DIM], q_s[2][SCHUNK][DIM], g_s[2][SCHUNK][2];
   pdl_wait();
-  const int s = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  const int s = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31;
   const int slot = b.slot_ids[s];
   const int t0 = b.cu_q[s], t1 = b.cu_q[s + 1];
   if (slot < 0 || t1 <= t0) return;
+  const bool loader = threadIdx.x >= 32;
+  const float qscale = 1.0f / sqrtf((float)DIM);
+  const T* proj = (const T*)a.proj;
+  auto fetch = [&](int buf, int tc, int tid, int nthreads) {
+    const int n = min(SCHUNK, t1 - tc);
+    for (int x = tid; x < n * DIM; x += nthreads) {
+      const int tt = x / DIM, d = x - tt * DIM;
+      const T* rowp = proj + (size_t)(tc + tt) * a.ld;
+      q_s[buf][tt][d] = to_f32(rowp[head * DIM + d]) * qscale;
+      k_s[buf][tt][d] = to_f32(rowp[a.H * DIM + head * DIM + d]);
+    }
+    for (int tt = tid; tt < n; tt += nthreads) {
+      const float zi = a.gates[(size_t)(tc + tt) * a.gld + head] + a.bi[head];
+      const float zf = a.gates[(size_t)(tc + tt) * a.gld + a.H + head] + a.bf[head];
+      g_s[buf][tt][0] = a.cap * tanhf(zi / a.cap);
+      g_s[buf][tt][1] = logsigmoid_f(a.cap * tanhf(zf / a.cap));
+    }
+  };
   float* base = a.state + (size_t)slot * a.state_stride;
   float* ng = base + a.n_off + (size_t)head * DIM;
   float nn[NPL];
 #pragma unroll
   for (int i = 0; i < NPL; ++i) nn[i] = lane + 32 * i < DIM ? ng[lane + 32 * i] : 0.f;
   float m = base[a.m_off + head];
-  const float qscale = 1.0f / sqrtf((float)DIM);
-  const T* proj = (const T*)a.proj;
-  for (int tc = t0; tc < t1; tc += CHUNK) {
-    const int n = min(CHUNK, t1 - tc);
-    float kq[CHUNK][NPL][2], gi[CHUNK], gf[CHUNK];
-#pragma unroll
-    for (int tt = 0; tt < CHUNK; ++tt) {
-      if (tt < n) {
-        const T* rowp = proj + (size_t)(tc + tt) * a.ld;
-#pragma unroll
-        for (int i = 0; i < NPL; ++i) {
-          const int d = lane + 32 * i;
-          kq[tt][i][0] = d < DIM ? to_f32(rowp[a.H * DIM + head * DIM + d]) : 0.f;
-          kq[tt][i][1] = d < DIM ? to_f32(rowp[head * DIM + d]) * qscale : 0.f;
-        }
-        gi[tt] = a.gates[(size_t)(tc + tt) * a.gld + head] + a.bi[head];
-        gf[tt] = a.gates[(size_t)(tc + tt) * a.gld + a.H + head] + a.bf[head];
-      }
-    }
-#pragma unroll
-    for (int tt = 0; tt < CHUNK; ++tt) {
-      if (tt < n) {
-        const float li = a.cap * tanhf(gi[tt] / a.cap);
-        const float lf = logsigmoid_f(a.cap * tanhf(gf[tt] / a.cap));
+  fetch(0, t0, threadIdx.x, blockDim.x);
+  __syncthreads();
+  int buf = 0;
+  for (int tc = t0; tc < t1; tc += SCHUNK, buf ^= 1) {
+    const int n = min(SCHUNK, t1 - tc);
+    if (loader) {
+      if (tc + SCHUNK < t1) fetch(buf ^ 1, tc + SCHUNK, threadIdx.x - 32, blockDim.x - 32);
+    } else {
+      for (int tt = 0; tt < n; ++tt) {
+        const float li = g_s[buf][tt][0], lf = g_s[buf][tt][1];
         const float m_new = fmaxf(lf + m, li);
         const float ea = expf(lf + m - m_new), eb = expf(li - m_new);
         m = m_new;
         float nq = 0.f;
 #pragma unroll
         for (int i = 0; i < NPL; ++i) {
-          nn[i] = fmaf(ea, nn[i], eb * kq[tt][i][0]);
-          nq = fmaf(nn[i], kq[tt][i][1], nq);
+          const int d = lane + 32 * i;
+          if (d < DIM) {
+            nn[i] = fmaf(ea, nn[i], eb * k_s[buf][tt][d]);
+            nq = fmaf(nn[i], q_s[buf][tt][d], nq);
+          }
         }
         nq = warp_sum(nq);
         if (lane == 0) {
@@ -193,23 +221,45 @@ __global__ void __launch_bounds__(32) mlstm_scan_kernel(MlstmArgs a, IertBatchVi
         }
       }
     }
+    __syncthreads();
   }
+  if (!loader) {
 #pragma unroll
-  for (int i = 0; i < NPL; ++i) if (lane + 32 * i < DIM) ng[lane + 32 * i] = nn[i];
-  if (lane == 0) base[a.m_off + head] = m;
+    for (int i = 0; i < NPL; ++i) if (lane + 32 * i < DIM) ng[lane + 32 * i] = nn[i];
+    if (lane == 0) base[a.m_off + head] = m;
+  }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256) mlstm_recur_kernel(MlstmArgs a, IertBatchView b) {
-  __shared__ float k_s[CHUNK][DIM], q_s[CHUNK][DIM], v_s[CHUNK][256], c_s[CHUNK][3];
+template <typename T, int R>
+__global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a, IertBatchView b) {
+  constexpr int RPT = (DIM + R - 1) / R;
+  __shared__ float k_s[2][CHUNK][DIM], q_s[2][CHUNK][DIM], v_s[2][CHUNK][256], c_s[2][CHUNK][3];
   pdl_wait();
   const int s = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * a.cols;
   const int slot = b.slot_ids[s];
   const int t0 = b.cu_q[s], t1 = b.cu_q[s + 1];
   if (slot < 0 || t1 <= t0) return;
+  const int workers = blockDim.x - LOADERS;
+  const bool loader = (int)threadIdx.x >= workers;
   const int col = threadIdx.x / R, r = threadIdx.x % R;
   const int j = c0 + col;
-  const bool live = col < a.cols && j < a.V;
+  const bool live = !loader && col < a.cols && j < a.V;
+  const float qscale = 1.0f / sqrtf((float)DIM);
+  const T* proj = (const T*)a.proj;
+  auto fetch = [&](int buf, int tc, int tid, int nthreads) {
+    const int n = min(CHUNK, t1 - tc);
+    for (int x = tid; x < n * DIM; x += nthreads) {
+      const int tt = x / DIM, d = x - tt * DIM;
+      const T* rowp = proj + (size_t)(tc + tt) * a.ld;
+      q_s[buf][tt][d] = to_f32(rowp[head * DIM + d]) * qscale;
+      k_s[buf][tt][d] = to_f32(rowp[a.H * DIM + head * DIM + d]);
+    }
+    for (int x = tid; x < n * a.cols; x += nthreads) {
+      const int tt = x / a.cols, cc = x - tt * a.cols;
+      v_s[buf][tt][cc] = c0 + cc < a.V ? to_f32(proj[(size_t)(tc + tt) * a.ld + 2 * a.H * DIM + head * a.V + c0 + cc]) : 0.f;
+    }
+    if (tid < n * 3) c_s[buf][tid / 3][tid % 3] = a.coef[((size_t)(tc + tid / 3) * a.H + head) * 3 + tid % 3];
+  };
   float* Sg = a.state + (size_t)slot * a.state_stride + a.s_off + (size_t)head * DIM * a.V;
   float S[RPT];
 #pragma unroll
@@ -217,38 +267,30 @@ __global__ void __launch_bounds__(256) mlstm_recur_kernel(MlstmArgs a, IertBatch
     const int d = r * RPT + i;
     S[i] = (live && d < DIM) ? Sg[(size_t)d * a.V + j] : 0.f;
   }
-  const float qscale = 1.0f / sqrtf((float)DIM);
-  const T* proj = (const T*)a.proj;
-  for (int tc = t0; tc < t1; tc += CHUNK) {
+  fetch(0, t0, threadIdx.x, blockDim.x);
+  __syncthreads();
+  int buf = 0;
+  for (int tc = t0; tc < t1; tc += CHUNK, buf ^= 1) {
     const int n = min(CHUNK, t1 - tc);
-    __syncthreads();
-    for (int x = threadIdx.x; x < n * DIM; x += blockDim.x) {
-      const int tt = x / DIM, d = x - tt * DIM;
-      const T* rowp = proj + (size_t)(tc + tt) * a.ld;
-      q_s[tt][d] = to_f32(rowp[head * DIM + d]) * qscale;
-      k_s[tt][d] = to_f32(rowp[a.H * DIM + head * DIM + d]);
-    }
-    for (int x = threadIdx.x; x < n * a.cols; x += blockDim.x) {
-      const int tt = x / a.cols, cc = x - tt * a.cols;
-      v_s[tt][cc] = c0 + cc < a.V ? to_f32(proj[(size_t)(tc + tt) * a.ld + 2 * a.H * DIM + head * a.V + c0 + cc]) : 0.f;
-    }
-    if (threadIdx.x < n * 3)
-      c_s[threadIdx.x / 3][threadIdx.x % 3] = a.coef[((size_t)(tc + threadIdx.x / 3) * a.H + head) * 3 + threadIdx.x % 3];
-    __syncthreads();
-    for (int tt = 0; tt < n; ++tt) {
-      const float ea = c_s[tt][0], eb = c_s[tt][1], den = c_s[tt][2];
-      const float bv = eb * (live ? v_s[tt][col] : 0.f);
-      float oq = 0.f;
+    if (loader) {
+      if (tc + CHUNK < t1) fetch(buf ^ 1, tc + CHUNK, threadIdx.x - workers, LOADERS);
+    } else {
+      for (int tt = 0; tt < n; ++tt) {
+        const float ea = c_s[buf][tt][0], eb = c_s[buf][tt][1], den = c_s[buf][tt][2];
+        const float bv = eb * (live ? v_s[buf][tt][col] : 0.f);
+        float oq = 0.f;
 #pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const int d = r * RPT + i;
-        const float kd = d < DIM ? k_s[tt][d] : 0.f, qd = d < DIM ? q_s[tt][d] : 0.f;
-        S[i] = fmaf(ea, S[i], kd * bv);
-        oq = fmaf(S[i], qd, oq);
+        for (int i = 0; i < RPT; ++i) {
+          const int d = r * RPT + i;
+          const float kd = d < DIM ? k_s[buf][tt][d] : 0.f, qd = d < DIM ? q_s[buf][tt][d] : 0.f;
+          S[i] = fmaf(ea, S[i], kd * bv);
+          oq = fmaf(S[i], qd, oq);
+        }
+        oq = group_sum<R>(oq);
+        if (live && r == 0) a.o[(size_t)(tc + tt) * a.H * a.V + (size_t)head * a.V + j] = oq / den;
       }
-      oq = group_sum(oq);
-      if (live && r == 0) a.o[(size_t)(tc + tt) * a.H * a.V + (size_t)head * a.V + j] = oq / den;
     }
+    __syncthreads();
   }
   if (live) {
 #pragma unroll
@@ -259,28 +301,42 @@ __global__ void __launch_bounds__(256) mlstm_recur_kernel(MlstmArgs a, IertBatch
   }
 }
 
-// Columns per CTA: as many CTAs as fill the device a few times over, not fewer than 8 columns each.
-int pick_cols(int n_seqs, int H, int V) {
-  int cols = MAX_COLS < V ? MAX_COLS : V;
-  const int want = 2 * iert_sm_count_cached();
-  while (cols > 8 && (long long)n_seqs * H * ((V + cols - 1) / cols) < want) cols = (cols + 1) / 2;
-  return cols;
+// Lanes per column: the fewest that give the device about eight warps per SM (at most 32), and columns per
+// CTA so that a CTA has up to 256 threads.
+struct Split { int lanes, cols; };
+Split pick_split(int n_seqs, int H, int V) {
+  const long long want = 8LL * 32 * iert_sm_count_cached();          // threads
+  int lanes = R_MIN;
+  while (lanes < 32 && (long long)n_seqs * H * V * lanes < want) lanes *= 2;
+  int cols = 256 / lanes;
+  if (cols > V) cols = V;
+  return {lanes, cols};
 }
 
 }  // namespace
 
 IERT_API int iert_recurrent_dim() { return DIM; }
 
+#define IERT_BY_LANES(L, CALL)                                       \
+  switch (L) {                                                       \
+    case 1: { constexpr int RR = 1 < R_MIN ? R_MIN : 1; CALL; } break;    \
+    case 2: { constexpr int RR = 2 < R_MIN ? R_MIN : 2; CALL; } break;    \
+    case 4: { constexpr int RR = 4 < R_MIN ? R_MIN : 4; CALL; } break;    \
+    case 8: { constexpr int RR = 8 < R_MIN ? R_MIN : 8; CALL; } break;    \
+    case 16: { constexpr int RR = 16 < R_MIN ? R_MIN : 16; CALL; } break; \
+    default: { constexpr int RR = 32; CALL; } break;                 \
+  }
+
 IERT_API int iert_delta_recur(const float* qkv, const float* beta, const float* decay, float* state,
                               long long state_stride, long long s_off, float* o, int G, int H, int V,
                               const IertBatchView* batch, cudaStream_t stream) {
   if (batch->n_seqs <= 0 || batch->n_tokens <= 0) return IERT_OK;
   if (G <= 0 || H <= 0 || H % G || V <= 0 || H > 65535) return IERT_BAD_ARGUMENT;
-  const int cols = pick_cols(batch->n_seqs, H, V);
-  DeltaArgs a = {qkv, beta, decay, state, state_stride, s_off, o, G, H, V, cols};
-  dim3 grid(batch->n_seqs, H, (V + cols - 1) / cols);
-  const int threads = ((cols * R + 31) / 32) * 32;
-  launch_dep(delta_recur_kernel, grid, dim3(threads), 0, stream, a, *batch);
+  const Split sp = pick_split(batch->n_seqs, H, V);
+  DeltaArgs a = {qkv, beta, decay, state, state_stride, s_off, o, G, H, V, sp.cols};
+  dim3 grid(batch->n_seqs, H, (V + sp.cols - 1) / sp.cols);
+  const int threads = ((sp.cols * sp.lanes + 31) / 32) * 32 + LOADERS;
+  IERT_BY_LANES(sp.lanes, launch_dep(delta_recur_kernel<RR>, grid, dim3(threads), 0, stream, a, *batch));
   return iert_check_launch("delta_recur");
 }
 
@@ -290,16 +346,16 @@ IERT_API int iert_mlstm_recur(const void* proj, int dtype, long long ld, const f
                               const IertBatchView* batch, cudaStream_t stream) {
   if (batch->n_seqs <= 0 || batch->n_tokens <= 0) return IERT_OK;
   if (H <= 0 || V <= 0 || H > 65535 || !(cap > 0.f) || (dtype != IERT_F32 && dtype != IERT_BF16)) return IERT_BAD_ARGUMENT;
-  const int cols = pick_cols(batch->n_seqs, H, V);
-  MlstmArgs a = {proj, ld, gates, gld, bi, bf, cap, state, state_stride, s_off, n_off, m_off, coef, o, H, V, cols};
-  dim3 grid(batch->n_seqs, H, (V + cols - 1) / cols);
-  const int threads = ((cols * R + 31) / 32) * 32;
+  const Split sp = pick_split(batch->n_seqs, H, V);
+  MlstmArgs a = {proj, ld, gates, gld, bi, bf, cap, state, state_stride, s_off, n_off, m_off, coef, o, H, V, sp.cols};
+  dim3 grid(batch->n_seqs, H, (V + sp.cols - 1) / sp.cols);
+  const int threads = ((sp.cols * sp.lanes + 31) / 32) * 32 + LOADERS;
   if (dtype == IERT_F32) {
-    launch_dep(mlstm_scan_kernel<float>, dim3(batch->n_seqs, H), dim3(32), 0, stream, a, *batch);
-    launch_dep(mlstm_recur_kernel<float>, grid, dim3(threads), 0, stream, a, *batch);
+    launch_dep(mlstm_scan_kernel<float>, dim3(batch->n_seqs, H), dim3(128), 0, stream, a, *batch);
+    IERT_BY_LANES(sp.lanes, (launch_dep(mlstm_recur_kernel<float, RR>, grid, dim3(threads), 0, stream, a, *batch)));
   } else {
-    launch_dep(mlstm_scan_kernel<__nv_bfloat16>, dim3(batch->n_seqs, H), dim3(32), 0, stream, a, *batch);
-    launch_dep(mlstm_recur_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, a, *batch);
+    launch_dep(mlstm_scan_kernel<__nv_bfloat16>, dim3(batch->n_seqs, H), dim3(128), 0, stream, a, *batch);
+    IERT_BY_LANES(sp.lanes, (launch_dep(mlstm_recur_kernel<__nv_bfloat16, RR>, grid, dim3(threads), 0, stream, a, *batch)));
   }
   return iert_check_launch("mlstm_recur");
 }

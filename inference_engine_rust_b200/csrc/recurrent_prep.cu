@@ -38,20 +38,28 @@ struct DeltaPrepArgs {
   int G, D, H, V, taps;
 };
 
+// One block per (token, unit), a unit being a q head, a k head or a v head: few channels per thread, so that
+// a step of a handful of tokens still spreads over the device and no thread walks a long list of loads.
 template <typename T>
-__global__ void delta_prep_kernel(DeltaPrepArgs a, IertBatchView b) {
-  extern __shared__ float row[];           // [C]
+__global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepArgs a, IertBatchView b) {
+  extern __shared__ float row[];           // [max(D, V)]
+  __shared__ float scratch[33];
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, unit = blockIdx.y;
   const int s = sequence_of_token(b, t);
   const int slot = s >= 0 ? b.slot_ids[s] : -1;
   if (slot < 0) return;
   const int GD = a.G * a.D, C = 2 * GD + a.H * a.V, taps = a.taps;
+  const bool is_v = unit >= 2 * a.G;
+  const int c0 = is_v ? 2 * GD + (unit - 2 * a.G) * a.V : unit * a.D;      // q heads, then k heads, lie back to back
+  const int n = is_v ? a.V : a.D;
   const int q_begin = b.cu_q[s], q_end = b.cu_q[s + 1];
   const int pos = b.pos0[s] + (t - q_begin);
   const T* proj = (const T*)a.proj;
   float* ring = a.state + (size_t)slot * a.state_stride + a.conv_off;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int c = c0 + i;
     float acc = 0.f;
     for (int j = taps - 1; j >= 0; --j) {          // oldest first
       const int tj = t - j;
@@ -60,29 +68,25 @@ __global__ void delta_prep_kernel(DeltaPrepArgs a, IertBatchView b) {
       else if (pos - j >= 0) x = ring[(size_t)((pos - j) % taps) * C + c];
       acc = fmaf(a.conv_w[(size_t)c * taps + (taps - 1 - j)], x, acc);
     }
-    row[c] = silu_f(acc);
-    if (t >= q_end - taps)                          // the sequence's newest inputs are its history
-      ring[(size_t)(pos % taps) * C + c] = to_f32(proj[(size_t)t * a.ld + c]);
+    const float v = silu_f(acc);
+    row[i] = v;
+    ss = fmaf(v, v, ss);
   }
-  __syncthreads();
-  // unit vectors: one warp per (q or k, head)
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int v = warp; v < 2 * a.G; v += nwarps) {
-    float* x = row + (size_t)v * a.D;
-    float ss = 0.f;
-    for (int d = lane; d < a.D; d += 32) ss = fmaf(x[d], x[d], ss);
-    ss = warp_sum(ss);
-    float f = 1.0f / sqrtf(ss + 1e-6f);
-    if (v < a.G) f *= 1.0f / sqrtf((float)a.D);
-    for (int d = lane; d < a.D; d += 32) x[d] *= f;
+  if (t >= q_end - taps)                            // the sequence's newest inputs are its history (a pass of its
+    for (int i = threadIdx.x; i < n; i += blockDim.x)   // own, so that the loads above do not queue behind stores)
+      ring[(size_t)(pos % taps) * C + c0 + i] = to_f32(proj[(size_t)t * a.ld + c0 + i]);
+  float f = 1.f;
+  if (!is_v) {                                      // unit vectors; q also times dim^-1/2
+    f = 1.0f / sqrtf(block_sum(ss, scratch) + 1e-6f);
+    if (unit < a.G) f *= 1.0f / sqrtf((float)a.D);
   }
-  __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) a.qkv[(size_t)t * C + c] = row[c];
-  for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
-    const float gb = a.gates[(size_t)t * a.gld + h], ga = a.gates[(size_t)t * a.gld + a.H + h];
-    a.beta[(size_t)t * a.H + h] = sigmoid_f(gb);
-    a.decay[(size_t)t * a.H + h] = expf(-expf(a.A_log[h]) * softplus_f(ga + a.dt_bias[h]));
-  }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) a.qkv[(size_t)t * C + c0 + i] = row[i] * f;
+  if (unit == 0)
+    for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
+      const float gb = a.gates[(size_t)t * a.gld + h], ga = a.gates[(size_t)t * a.gld + a.H + h];
+      a.beta[(size_t)t * a.H + h] = sigmoid_f(gb);
+      a.decay[(size_t)t * a.H + h] = expf(-expf(a.A_log[h]) * softplus_f(ga + a.dt_bias[h]));
+    }
 }
 
 // o [T, H*V] fp32; gate: column gate_off + h*V + e of the packed projection; weight index
@@ -117,12 +121,14 @@ IERT_API int iert_delta_prep(const void* proj, int dtype, long long ld, const fl
                              int G, int D, int H, int V, int taps, const IertBatchView* batch, cudaStream_t stream) {
   if (batch->n_tokens <= 0) return IERT_OK;
   const long long C = 2LL * G * D + (long long)H * V;
-  if (G <= 0 || D <= 0 || H <= 0 || V <= 0 || taps <= 0 || C > 11000) return IERT_BAD_ARGUMENT;
+  if (G <= 0 || D <= 0 || H <= 0 || V <= 0 || taps <= 0 || D > 11000 || V > 11000 || 2 * G + H > 65535) return IERT_BAD_ARGUMENT;
   DeltaPrepArgs a = {proj, ld, gates, gld, conv_w, A_log, dt_bias, state, state_stride, conv_off, qkv, beta, decay,
                      G, D, H, V, taps};
-  const size_t smem = (size_t)C * sizeof(float);
-  if (dtype == IERT_F32) launch_dep(delta_prep_kernel<float>, dim3(batch->n_tokens), dim3(256), smem, stream, a, *batch);
-  else if (dtype == IERT_BF16) launch_dep(delta_prep_kernel<__nv_bfloat16>, dim3(batch->n_tokens), dim3(256), smem, stream, a, *batch);
+  (void)C;
+  const size_t smem = (size_t)(D > V ? D : V) * sizeof(float);
+  const dim3 grid(batch->n_tokens, 2 * G + H);
+  if (dtype == IERT_F32) launch_dep(delta_prep_kernel<float>, grid, dim3(128), smem, stream, a, *batch);
+  else if (dtype == IERT_BF16) launch_dep(delta_prep_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, a, *batch);
   else return IERT_BAD_ARGUMENT;
   return iert_check_launch("delta_prep");
 }

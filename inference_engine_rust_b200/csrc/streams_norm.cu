@@ -54,33 +54,62 @@ __global__ void streams_norm_kernel(StreamsNormArgs a) {
   float* xr = a.xs + (size_t)row * S * H;
   float* yr = a.y ? a.y + (size_t)row * H : nullptr;
   float part = 0.f;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    float x[MAX_STREAMS];
+  // four columns per thread and pass (16-byte accesses) when the row length allows
+  const int W = (H % 4 == 0) ? 4 : 1;
+  for (int h = threadIdx.x * W; h < H; h += blockDim.x * W) {
+    float x[MAX_STREAMS][4], yv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (W == 4) {
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s) x[s] = s < S ? xr[(size_t)s * H + h] : 0.f;
-    if (a.update) {
-      const float yv = yr[h];
-      float nx[MAX_STREAMS];
-#pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t) {
-        float v = 0.f;
-        if (t < S) {
-#pragma unroll
-          for (int s = 0; s < MAX_STREAMS; ++s) if (s < S) v = fmaf(mix[s * S + t], x[s], v);
-          v = fmaf(outc[t], yv, v);
-          if (a.write_back) xr[(size_t)t * H + h] = v;
+      for (int s = 0; s < MAX_STREAMS; ++s)
+        if (s < S) {
+          const float4 v = *reinterpret_cast<const float4*>(xr + (size_t)s * H + h);
+          x[s][0] = v.x; x[s][1] = v.y; x[s][2] = v.z; x[s][3] = v.w;
         }
-        nx[t] = v;
+      if (a.update) {
+        const float4 v = *reinterpret_cast<const float4*>(yr + h);
+        yv[0] = v.x; yv[1] = v.y; yv[2] = v.z; yv[3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int s = 0; s < MAX_STREAMS; ++s) if (s < S) x[s][0] = xr[(size_t)s * H + h];
+      if (a.update) yv[0] = yr[h];
+    }
+    float u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (e >= W) break;
+      if (a.update) {
+        float nx[MAX_STREAMS];
+#pragma unroll
+        for (int t = 0; t < MAX_STREAMS; ++t) {
+          float v = 0.f;
+          if (t < S) {
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s) if (s < S) v = fmaf(mix[s * S + t], x[s][e], v);
+            v = fmaf(outc[t], yv[e], v);
+          }
+          nx[t] = v;
+        }
+#pragma unroll
+        for (int t = 0; t < MAX_STREAMS; ++t) x[t][e] = nx[t];
       }
 #pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t) x[t] = nx[t];
+      for (int s = 0; s < MAX_STREAMS; ++s) if (s < S) u[e] = fmaf(inc[s], x[s][e], u[e]);
+      u_row[h + e] = u[e];
+      part += u[e];
     }
-    if (a.zero_y && yr) yr[h] = 0.f;
-    float u = 0.f;
+    if (a.update && a.write_back) {
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s) if (s < S) u = fmaf(inc[s], x[s], u);
-    u_row[h] = u;
-    part += u;
+      for (int t = 0; t < MAX_STREAMS; ++t)
+        if (t < S) {
+          if (W == 4) *reinterpret_cast<float4*>(xr + (size_t)t * H + h) = make_float4(x[t][0], x[t][1], x[t][2], x[t][3]);
+          else xr[(size_t)t * H + h] = x[t][0];
+        }
+    }
+    if (a.zero_y && yr) {
+      if (W == 4) *reinterpret_cast<float4*>(yr + h) = make_float4(0.f, 0.f, 0.f, 0.f);
+      else yr[h] = 0.f;
+    }
   }
   if (a.sum_out)
     for (int h = threadIdx.x; h < H; h += blockDim.x) a.sum_out[(size_t)blockIdx.x * H + h] = u_row[h];

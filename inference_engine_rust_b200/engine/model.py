@@ -59,6 +59,12 @@ class Model:
         other (a bias "b", say) under that name + "." + its local name."""
         return {local: weight_name if local == "weight" else f"{weight_name}.{local}" for local in norm.tensor_specs()}
 
+    @staticmethod
+    def _block_specs(block) -> Dict[str, TensorSpec]:
+        """Tensors of a block arrangement's own (most have none, and need not say so)."""
+        specs = getattr(block, "tensor_specs", None)
+        return specs() if specs is not None else {}
+
     def _norm_specs(self, norm, weight_name: str) -> Dict[str, TensorSpec]:
         specs = norm.tensor_specs()
         return {name: specs[local] for local, name in self._norm_names(norm, weight_name).items()}
@@ -86,7 +92,7 @@ class Model:
                     out[ls.ffn_prefix + local] = ts
             for role, norm in extra.items():
                 out.update(self._norm_specs(norm, ls.extra_norms[role][1]))
-            for local, ts in block.tensor_specs().items():        # an arrangement with tensors of its own
+            for local, ts in self._block_specs(block).items():    # an arrangement with tensors of its own
                 out[ls.block_prefix + local] = ts
         return out
 
@@ -141,8 +147,8 @@ class Model:
                 ffn.load({local: get(ls.ffn_prefix + local) for local in ffn.tensor_specs()})
             for role, norm in extra.items():
                 load_norm(norm, ls.extra_norms[role][1])
-            if block.tensor_specs():
-                block.load({local: get(ls.block_prefix + local) for local in block.tensor_specs()})
+            if self._block_specs(block):
+                block.load({local: get(ls.block_prefix + local) for local in self._block_specs(block)})
         self.loaded = True
 
     def load_random(self, seed: int, std: float = 0.02, on_device: bool = False) -> None:

@@ -740,9 +740,9 @@ def test_another_output_head_is_registered_and_used(dtype):
     want = torch.tanh(plain / cap) * cap
     assert ((plain - want).abs() > 0.1 * cap).any(), "the cap never binds: the test would not see a head that ignores it"
 
-    register_part("head", "softcap", _soft_cap_head())
+    register_part("head", "toy_softcap", _soft_cap_head())
     register_architecture("CappedToyForCausalLM", CappedConfig,
-                          lambda cfg: dataclasses.replace(build_spec(cfg), head=PartSpec("softcap", {"cap": cap})))
+                          lambda cfg: dataclasses.replace(build_spec(cfg), head=PartSpec("toy_softcap", {"cap": cap})))
     try:
         raw = dict(TINY_B, architectures=["CappedToyForCausalLM"])
         model = LoadedModel.random(raw, seed=12, dtype=dtype, std=WEIGHT_STD)
@@ -755,7 +755,7 @@ def test_another_output_head_is_registered_and_used(dtype):
         eng.check_device()
         compare(torch.cat(got), want, dtype, "capped head")
     finally:
-        unregister_part("head", "softcap")
+        unregister_part("head", "toy_softcap")
         registry._ARCHITECTURES.pop("CappedToyForCausalLM", None)
 
 
