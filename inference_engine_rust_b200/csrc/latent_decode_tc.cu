@@ -314,21 +314,30 @@ latent_decode_merge_kernel(const float* __restrict__ part_m, const float* __rest
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int e = warp; e < V; e += THREADS / 32) {      // rank is a multiple of 32: 16-byte loads of eight weights
-    const T* w = w_uv + ((size_t)h * V + e) * rank;
-    float a = 0.f;
+  // rank is a multiple of 32: 16-byte loads of eight weights; four rows' loads are issued before the first is used
+  for (int e0 = warp * 4; e0 < V; e0 += (THREADS / 32) * 4) {
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
     for (int r = lane * 8; r < rank; r += 32 * 8) {
-      const uint4 v = *reinterpret_cast<const uint4*>(w + r);
-      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+      uint4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        v[k] = e0 + k < V ? *reinterpret_cast<const uint4*>(w_uv + ((size_t)h * V + e0 + k) * rank + r) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(p[k]);
-        a = fmaf(f.x, lat[r + 2 * k], a);
-        a = fmaf(f.y, lat[r + 2 * k + 1], a);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float2 f = __bfloat1622float2(p[c]);
+          a[k] = fmaf(f.x, lat[r + 2 * c], a[k]);
+          a[k] = fmaf(f.y, lat[r + 2 * c + 1], a[k]);
+        }
       }
     }
-    a = warp_sum(a);
-    if (lane == 0) o[e] = from_f32<T>(a);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float sum = warp_sum(a[k]);
+      if (lane == 0 && e0 + k < V) o[e0 + k] = from_f32<T>(sum);
+    }
   }
 }
 

@@ -2,8 +2,9 @@
 // sequence's state.  Compiled per key size (-DDIM=...), like the attention kernels per head size.
 //
 // Work split: a column j of S never meets another column, so a CTA owns (sequence, head, a run of
-// columns) and a thread owns RPT = ceil(DIM / R) rows of one column in registers; the R threads of a
-// column are neighbouring lanes and add their partial dot products by shuffles.  R is chosen at the
+// columns) and a thread owns RPT = ceil(DIM / R) rows of one column in registers (rows r, r + R, ...: the
+// lanes of a column read neighbouring words of a token's k and q, so shared memory serves them without bank
+// conflicts); the R threads of a column are neighbouring lanes and add their partial dot products by shuffles.  R is chosen at the
 // launch: the tokens of a sequence are a chain, so all the parallelism there is lies in heads x columns x
 // R, and a single prompt wants many lanes per column (more warps per SM to hide the chain's latency)
 // where a batch of sequences is served best by few (fewer shuffles and shared-memory reads per FMA).
@@ -56,7 +57,7 @@ struct DeltaArgs {
 template <int R>
 __global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a, IertBatchView b) {
   constexpr int RPT = (DIM + R - 1) / R;
-  __shared__ float k_s[2][CHUNK][DIM], q_s[2][CHUNK][DIM], v_s[2][CHUNK][256], bg_s[2][CHUNK][2];
+  __shared__ __align__(16) float k_s[2][CHUNK][DIM], q_s[2][CHUNK][DIM], v_s[2][CHUNK][256], bg_s[2][CHUNK][2];
   pdl_wait();
   const int s = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * a.cols;
   const int slot = b.slot_ids[s];
@@ -71,11 +72,20 @@ __global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a,
   const int GD = a.G * DIM, C = 2 * GD + a.H * a.V;
   auto fetch = [&](int buf, int tc, int tid, int nthreads) {
     const int n = min(CHUNK, t1 - tc);
-    for (int x = tid; x < n * DIM; x += nthreads) {
-      const int tt = x / DIM, d = x - tt * DIM;
-      const float* rowp = a.qkv + (size_t)(tc + tt) * C;
-      q_s[buf][tt][d] = rowp[g * DIM + d];
-      k_s[buf][tt][d] = rowp[GD + g * DIM + d];
+    if (DIM % 4 == 0 && C % 4 == 0 && ((uintptr_t)a.qkv & 15) == 0) {       // 16-byte loads
+      for (int x = tid; x < n * (DIM / 4); x += nthreads) {
+        const int tt = x / (DIM / 4), d = 4 * (x - tt * (DIM / 4));
+        const float* rowp = a.qkv + (size_t)(tc + tt) * C;
+        *reinterpret_cast<float4*>(&q_s[buf][tt][d]) = *reinterpret_cast<const float4*>(rowp + g * DIM + d);
+        *reinterpret_cast<float4*>(&k_s[buf][tt][d]) = *reinterpret_cast<const float4*>(rowp + GD + g * DIM + d);
+      }
+    } else {
+      for (int x = tid; x < n * DIM; x += nthreads) {
+        const int tt = x / DIM, d = x - tt * DIM;
+        const float* rowp = a.qkv + (size_t)(tc + tt) * C;
+        q_s[buf][tt][d] = rowp[g * DIM + d];
+        k_s[buf][tt][d] = rowp[GD + g * DIM + d];
+      }
     }
     for (int x = tid; x < n * a.cols; x += nthreads) {
       const int tt = x / a.cols, cc = x - tt * a.cols;
@@ -90,7 +100,7 @@ __global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a,
   float S[RPT];
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
-    const int d = r * RPT + i;
+    const int d = i * R + r;
     S[i] = (live && d < DIM) ? Sg[(size_t)d * a.V + j] : 0.f;
   }
   fetch(0, t0, threadIdx.x, blockDim.x);
@@ -107,7 +117,7 @@ __global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a,
         float dk = 0.f;
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
-          const int d = r * RPT + i;
+          const int d = i * R + r;
           kk[i] = d < DIM ? k_s[buf][tt][d] : 0.f;
           S[i] *= gd;
           dk = fmaf(S[i], kk[i], dk);
@@ -117,7 +127,7 @@ __global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a,
         float oq = 0.f;
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
-          const int d = r * RPT + i;
+          const int d = i * R + r;
           S[i] = fmaf(kk[i], u, S[i]);
           oq = fmaf(S[i], d < DIM ? q_s[buf][tt][d] : 0.f, oq);
         }
@@ -130,7 +140,7 @@ __global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a,
   if (live) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-      const int d = r * RPT + i;
+      const int d = i * R + r;
       if (d < DIM) Sg[(size_t)d * a.V + j] = S[i];
     }
   }
@@ -162,7 +172,7 @@ constexpr int SCHUNK = DIM <= 64 ? 32 : DIM <= 128 ? 16 : DIM <= 256 ? 8 : DIM <
 
 template <typename T>
 __global__ void __launch_bounds__(128) mlstm_scan_kernel(MlstmArgs a, IertBatchView b) {
-  __shared__ float k_s[2][SCHUNK][DIM], q_s[2][SCHUNK][DIM], g_s[2][SCHUNK][2];
+  __shared__ __align__(16) float k_s[2][SCHUNK][DIM], q_s[2][SCHUNK][DIM], g_s[2][SCHUNK][2];
   pdl_wait();
   const int s = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31;
   const int slot = b.slot_ids[s];
@@ -173,11 +183,29 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(MlstmArgs a, IertBatchV
   const T* proj = (const T*)a.proj;
   auto fetch = [&](int buf, int tc, int tid, int nthreads) {
     const int n = min(SCHUNK, t1 - tc);
-    for (int x = tid; x < n * DIM; x += nthreads) {
-      const int tt = x / DIM, d = x - tt * DIM;
-      const T* rowp = proj + (size_t)(tc + tt) * a.ld;
-      q_s[buf][tt][d] = to_f32(rowp[head * DIM + d]) * qscale;
-      k_s[buf][tt][d] = to_f32(rowp[a.H * DIM + head * DIM + d]);
+    if (sizeof(T) == 2 && DIM % 8 == 0 && a.ld % 8 == 0 && ((uintptr_t)a.proj & 15) == 0) {      // eight bf16 per load
+      for (int x = tid; x < n * (DIM / 8) * 2; x += nthreads) {
+        const int which = x & 1, y = x >> 1;
+        const int tt = y / (DIM / 8), d = 8 * (y - tt * (DIM / 8));
+        const T* src = proj + (size_t)(tc + tt) * a.ld + (which ? a.H * DIM : 0) + head * DIM + d;
+        const uint4 v = *reinterpret_cast<const uint4*>(src);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+        float* dst = which ? &k_s[buf][tt][d] : &q_s[buf][tt][d];
+        const float sc = which ? 1.f : qscale;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(p[e]);
+          dst[2 * e] = f.x * sc;
+          dst[2 * e + 1] = f.y * sc;
+        }
+      }
+    } else {
+      for (int x = tid; x < n * DIM; x += nthreads) {
+        const int tt = x / DIM, d = x - tt * DIM;
+        const T* rowp = proj + (size_t)(tc + tt) * a.ld;
+        q_s[buf][tt][d] = to_f32(rowp[head * DIM + d]) * qscale;
+        k_s[buf][tt][d] = to_f32(rowp[a.H * DIM + head * DIM + d]);
+      }
     }
     for (int tt = tid; tt < n; tt += nthreads) {
       const float zi = a.gates[(size_t)(tc + tt) * a.gld + head] + a.bi[head];
@@ -233,7 +261,7 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(MlstmArgs a, IertBatchV
 template <typename T, int R>
 __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a, IertBatchView b) {
   constexpr int RPT = (DIM + R - 1) / R;
-  __shared__ float k_s[2][CHUNK][DIM], q_s[2][CHUNK][DIM], v_s[2][CHUNK][256], c_s[2][CHUNK][3];
+  __shared__ __align__(16) float k_s[2][CHUNK][DIM], q_s[2][CHUNK][DIM], v_s[2][CHUNK][256], c_s[2][CHUNK][3];
   pdl_wait();
   const int s = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * a.cols;
   const int slot = b.slot_ids[s];
@@ -248,11 +276,29 @@ __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a,
   const T* proj = (const T*)a.proj;
   auto fetch = [&](int buf, int tc, int tid, int nthreads) {
     const int n = min(CHUNK, t1 - tc);
-    for (int x = tid; x < n * DIM; x += nthreads) {
-      const int tt = x / DIM, d = x - tt * DIM;
-      const T* rowp = proj + (size_t)(tc + tt) * a.ld;
-      q_s[buf][tt][d] = to_f32(rowp[head * DIM + d]) * qscale;
-      k_s[buf][tt][d] = to_f32(rowp[a.H * DIM + head * DIM + d]);
+    if (sizeof(T) == 2 && DIM % 8 == 0 && a.ld % 8 == 0 && ((uintptr_t)a.proj & 15) == 0) {      // eight bf16 per load
+      for (int x = tid; x < n * (DIM / 8) * 2; x += nthreads) {
+        const int which = x & 1, y = x >> 1;
+        const int tt = y / (DIM / 8), d = 8 * (y - tt * (DIM / 8));
+        const T* src = proj + (size_t)(tc + tt) * a.ld + (which ? a.H * DIM : 0) + head * DIM + d;
+        const uint4 v = *reinterpret_cast<const uint4*>(src);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+        float* dst = which ? &k_s[buf][tt][d] : &q_s[buf][tt][d];
+        const float sc = which ? 1.f : qscale;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(p[e]);
+          dst[2 * e] = f.x * sc;
+          dst[2 * e + 1] = f.y * sc;
+        }
+      }
+    } else {
+      for (int x = tid; x < n * DIM; x += nthreads) {
+        const int tt = x / DIM, d = x - tt * DIM;
+        const T* rowp = proj + (size_t)(tc + tt) * a.ld;
+        q_s[buf][tt][d] = to_f32(rowp[head * DIM + d]) * qscale;
+        k_s[buf][tt][d] = to_f32(rowp[a.H * DIM + head * DIM + d]);
+      }
     }
     for (int x = tid; x < n * a.cols; x += nthreads) {
       const int tt = x / a.cols, cc = x - tt * a.cols;
@@ -264,7 +310,7 @@ __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a,
   float S[RPT];
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
-    const int d = r * RPT + i;
+    const int d = i * R + r;
     S[i] = (live && d < DIM) ? Sg[(size_t)d * a.V + j] : 0.f;
   }
   fetch(0, t0, threadIdx.x, blockDim.x);
@@ -281,7 +327,7 @@ __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a,
         float oq = 0.f;
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
-          const int d = r * RPT + i;
+          const int d = i * R + r;
           const float kd = d < DIM ? k_s[buf][tt][d] : 0.f, qd = d < DIM ? q_s[buf][tt][d] : 0.f;
           S[i] = fmaf(ea, S[i], kd * bv);
           oq = fmaf(S[i], qd, oq);
@@ -295,7 +341,7 @@ __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a,
   if (live) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-      const int d = r * RPT + i;
+      const int d = i * R + r;
       if (d < DIM) Sg[(size_t)d * a.V + j] = S[i];
     }
   }

@@ -36,6 +36,7 @@ struct DeltaPrepArgs {
   float* beta;             // out [T, H]
   float* decay;            // out [T, H]
   int G, D, H, V, taps;
+  int tokens_per_block;    // a long step gives a block several tokens in turn
 };
 
 // One block per (token, unit), a unit being a q head, a k head or a v head: few channels per thread, so that
@@ -45,10 +46,12 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepArgs a, IertBa
   extern __shared__ float row[];           // [max(D, V)]
   __shared__ float scratch[33];
   pdl_wait();
-  const int t = blockIdx.x, unit = blockIdx.y;
+  const int unit = blockIdx.y;
+  for (int t = blockIdx.x * a.tokens_per_block; t < min(b.n_tokens, (int)(blockIdx.x + 1) * a.tokens_per_block); ++t) {
+  __syncthreads();                                   // `row` and `scratch` are free again
   const int s = sequence_of_token(b, t);
   const int slot = s >= 0 ? b.slot_ids[s] : -1;
-  if (slot < 0) return;
+  if (slot < 0) continue;
   const int GD = a.G * a.D, C = 2 * GD + a.H * a.V, taps = a.taps;
   const bool is_v = unit >= 2 * a.G;
   const int c0 = is_v ? 2 * GD + (unit - 2 * a.G) * a.V : unit * a.D;      // q heads, then k heads, lie back to back
@@ -87,6 +90,7 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepArgs a, IertBa
       a.beta[(size_t)t * a.H + h] = sigmoid_f(gb);
       a.decay[(size_t)t * a.H + h] = expf(-expf(a.A_log[h]) * softplus_f(ga + a.dt_bias[h]));
     }
+  }
 }
 
 // o [T, H*V] fp32; gate: column gate_off + h*V + e of the packed projection; weight index
@@ -123,10 +127,10 @@ IERT_API int iert_delta_prep(const void* proj, int dtype, long long ld, const fl
   const long long C = 2LL * G * D + (long long)H * V;
   if (G <= 0 || D <= 0 || H <= 0 || V <= 0 || taps <= 0 || D > 11000 || V > 11000 || 2 * G + H > 65535) return IERT_BAD_ARGUMENT;
   DeltaPrepArgs a = {proj, ld, gates, gld, conv_w, A_log, dt_bias, state, state_stride, conv_off, qkv, beta, decay,
-                     G, D, H, V, taps};
+                     G, D, H, V, taps, batch->n_tokens >= 1024 ? 8 : 1};
   (void)C;
   const size_t smem = (size_t)(D > V ? D : V) * sizeof(float);
-  const dim3 grid(batch->n_tokens, 2 * G + H);
+  const dim3 grid((batch->n_tokens + a.tokens_per_block - 1) / a.tokens_per_block, 2 * G + H);
   if (dtype == IERT_F32) launch_dep(delta_prep_kernel<float>, grid, dim3(128), smem, stream, a, *batch);
   else if (dtype == IERT_BF16) launch_dep(delta_prep_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, a, *batch);
   else return IERT_BAD_ARGUMENT;
