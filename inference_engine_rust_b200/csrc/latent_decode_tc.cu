@@ -257,20 +257,22 @@ latent_decode_tc_kernel(const __nv_bfloat16* __restrict__ qa, IertBatchView b, I
     }
 }
 
+constexpr int MERGE_THREADS = 256;
+
 template <typename T>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(MERGE_THREADS)
 latent_decode_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
                            const float* __restrict__ part_acc, int splits, int Hpad, int rank,
                            const float* __restrict__ sink, const T* __restrict__ w_uv, T* __restrict__ out,
                            IertBatchView b, int H, int V) {
   extern __shared__ float sm[];
   float* lat = sm;                 // [rank]
-  float* wgt = sm + rank;          // [splits]
+  float* wgt = sm + rank;          // [64]
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   T* o = out + ((size_t)t * H + h) * V;
   if (b.slot_ids[t] < 0) {
-    for (int e = threadIdx.x; e < V; e += THREADS) o[e] = from_f32<T>(0.f);
+    for (int e = threadIdx.x; e < V; e += MERGE_THREADS) o[e] = from_f32<T>(0.f);
     return;
   }
   if (threadIdx.x < 32) {                 // splits <= 64: two runs per lane
@@ -294,36 +296,36 @@ latent_decode_merge_kernel(const float* __restrict__ part_m, const float* __rest
     const float L = warp_sum(part) + (sink ? expf(snk - M) : 0.f);
     const float inv = L > 0.f ? 1.0f / L : 0.f;
 #pragma unroll
-    for (int k = 0; k < 2; ++k) if (lane + 32 * k < splits) wgt[lane + 32 * k] = w[k] * inv;
+    for (int k = 0; k < 2; ++k) wgt[lane + 32 * k] = lane + 32 * k < splits ? w[k] * inv : 0.f;
   }
   __syncthreads();
-  for (int r = threadIdx.x; r < rank; r += THREADS) {
+  // the runs' partial sums, eight loads in flight per thread; an empty run's row (weight 0) is never read
+  for (int r = threadIdx.x; r < rank; r += MERGE_THREADS) {
     float a = 0.f;
-    for (int i0 = 0; i0 < splits; i0 += 4) {          // four runs' loads in flight; an empty run's row is never read
-      float v[4];
+    for (int i0 = 0; i0 < splits; i0 += 8) {
+      float v[8];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < 8; ++k) {
         const int i = i0 + k;
-        const bool live = i < splits && wgt[i < splits ? i : 0] != 0.f;
-        v[k] = live ? part_acc[(((size_t)t * splits + i) * Hpad + h) * rank + r] : 0.f;
+        v[k] = (i < splits && wgt[i] != 0.f) ? part_acc[(((size_t)t * splits + i) * Hpad + h) * rank + r] : 0.f;
       }
 #pragma unroll
-      for (int k = 0; k < 4; ++k) if (i0 + k < splits) a = fmaf(wgt[i0 + k], v[k], a);
+      for (int k = 0; k < 8; ++k) a = fmaf(wgt[(i0 + k) & 63], v[k], a);
     }
     lat[r] = a;
   }
   __syncthreads();
+  // W_uv: rank is a multiple of 32, 16-byte loads of eight weights; eight rows' loads are issued before the first is used
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // rank is a multiple of 32: 16-byte loads of eight weights; four rows' loads are issued before the first is used
-  for (int e0 = warp * 4; e0 < V; e0 += (THREADS / 32) * 4) {
-    float a[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int e0 = warp * 8; e0 < V; e0 += (MERGE_THREADS / 32) * 8) {
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int r = lane * 8; r < rank; r += 32 * 8) {
-      uint4 v[4];
+      uint4 v[8];
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
+      for (int k = 0; k < 8; ++k)
         v[k] = e0 + k < V ? *reinterpret_cast<const uint4*>(w_uv + ((size_t)h * V + e0 + k) * rank + r) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < 8; ++k) {
         const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -334,7 +336,7 @@ latent_decode_merge_kernel(const float* __restrict__ part_m, const float* __rest
       }
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < 8; ++k) {
       const float sum = warp_sum(a[k]);
       if (lane == 0 && e0 + k < V) o[e0 + k] = from_f32<T>(sum);
     }
@@ -397,7 +399,7 @@ IERT_API int iert_latent_attention_decode_tc(const void* q, long long ldq, const
   else
     launch_dep(latent_decode_tc_kernel<1>, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)qa, *batch, *kv, Hpad,
                scale, splits, part_m, part_l, part_acc, err);
-  launch_dep(latent_decode_merge_kernel<__nv_bfloat16>, dim3(T, H), dim3(THREADS), (size_t)(rank + splits) * sizeof(float),
+  launch_dep(latent_decode_merge_kernel<__nv_bfloat16>, dim3(T, H), dim3(MERGE_THREADS), (size_t)(rank + 64) * sizeof(float),
              stream, (const float*)part_m, (const float*)part_l, (const float*)part_acc, splits, Hpad, rank, sink,
              (const __nv_bfloat16*)w_uv, (__nv_bfloat16*)out, *batch, H, V);
   return iert_check_launch("latent_attention_decode_tc");

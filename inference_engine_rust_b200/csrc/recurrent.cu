@@ -111,7 +111,9 @@ __global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a,
     if (loader) {
       if (tc + CHUNK < t1) fetch(buf ^ 1, tc + CHUNK, threadIdx.x - workers, LOADERS);
     } else {
-      for (int tt = 0; tt < n; ++tt) {
+#pragma unroll
+      for (int tt = 0; tt < CHUNK; ++tt) {
+        if (tt >= n) break;
         const float beta = bg_s[buf][tt][0], gd = bg_s[buf][tt][1];
         float kk[RPT];
         float dk = 0.f;
@@ -228,7 +230,9 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(MlstmArgs a, IertBatchV
     if (loader) {
       if (tc + SCHUNK < t1) fetch(buf ^ 1, tc + SCHUNK, threadIdx.x - 32, blockDim.x - 32);
     } else {
-      for (int tt = 0; tt < n; ++tt) {
+#pragma unroll 4
+      for (int tt = 0; tt < SCHUNK; ++tt) {
+        if (tt >= n) break;
         const float li = g_s[buf][tt][0], lf = g_s[buf][tt][1];
         const float m_new = fmaxf(lf + m, li);
         const float ea = expf(lf + m - m_new), eb = expf(li - m_new);
@@ -321,7 +325,9 @@ __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a,
     if (loader) {
       if (tc + CHUNK < t1) fetch(buf ^ 1, tc + CHUNK, threadIdx.x - workers, LOADERS);
     } else {
-      for (int tt = 0; tt < n; ++tt) {
+#pragma unroll
+      for (int tt = 0; tt < CHUNK; ++tt) {
+        if (tt >= n) break;
         const float ea = c_s[buf][tt][0], eb = c_s[buf][tt][1], den = c_s[buf][tt][2];
         const float bv = eb * (live ? v_s[buf][tt][col] : 0.f);
         float oq = 0.f;

@@ -95,9 +95,10 @@ __global__ void streams_norm_kernel(StreamsNormArgs a) {
       }
 #pragma unroll
       for (int s = 0; s < MAX_STREAMS; ++s) if (s < S) u[e] = fmaf(inc[s], x[s][e], u[e]);
-      u_row[h + e] = u[e];
       part += u[e];
     }
+    if (W == 4) *reinterpret_cast<float4*>(u_row + h) = make_float4(u[0], u[1], u[2], u[3]);
+    else u_row[h] = u[0];
     if (a.update && a.write_back) {
 #pragma unroll
       for (int t = 0; t < MAX_STREAMS; ++t)
@@ -116,9 +117,35 @@ __global__ void streams_norm_kernel(StreamsNormArgs a) {
   if (!a.out) return;
   const float mean = block_sum(part, scratch) / (float)H;
   float dev = 0.f;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) { const float d = u_row[h] - mean; dev = fmaf(d, d, dev); }
+  for (int h = threadIdx.x * W; h < H; h += blockDim.x * W) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (e >= W) break;
+      const float d = u_row[h + e] - mean;
+      dev = fmaf(d, d, dev);
+    }
+  }
   const float rstd = 1.0f / sqrtf(block_sum(dev, scratch) / (float)H + a.eps);
   TO* o = (TO*)a.out + (size_t)blockIdx.x * H;
+  if (W == 4) {                               // four outputs per thread and pass
+    for (int h = threadIdx.x * 4; h < H; h += blockDim.x * 4) {
+      const float4 u = *reinterpret_cast<const float4*>(u_row + h);
+      const float4 w = *reinterpret_cast<const float4*>(a.w + h);
+      const float4 bb = a.b ? *reinterpret_cast<const float4*>(a.b + h) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float v0 = (u.x - mean) * rstd * w.x + bb.x, v1 = (u.y - mean) * rstd * w.y + bb.y;
+      const float v2 = (u.z - mean) * rstd * w.z + bb.z, v3 = (u.w - mean) * rstd * w.w + bb.w;
+      if (sizeof(TO) == 4) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + h) = make_float4(v0, v1, v2, v3);
+      } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(o) + h) = pk;
+      }
+    }
+    return;
+  }
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     const float v = (u_row[h] - mean) * rstd * a.w[h] + (a.b ? a.b[h] : 0.f);
     o[h] = from_f32<TO>(v);
