@@ -36,22 +36,22 @@ struct DeltaPrepArgs {
   float* beta;             // out [T, H]
   float* decay;            // out [T, H]
   int G, D, H, V, taps;
-  int tokens_per_block;    // a long step gives a block several tokens in turn
 };
 
-// One block per (token, unit), a unit being a q head, a k head or a v head: few channels per thread, so that
-// a step of a handful of tokens still spreads over the device and no thread walks a long list of loads.
+// One warp per (token, unit), a unit being a q head, a k head or a v head: a lane has a few channels, all its
+// loads are independent, and the unit norm is a warp sum: no shared memory, no block barrier, and a step
+// of a handful of tokens still spreads over the device.  A block is four tokens of one unit.
+constexpr int PREP_MAX_PER_LANE = 16;      // channels of a unit per lane kept in registers (units up to 512 wide)
+
 template <typename T>
 __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepArgs a, IertBatchView b) {
-  extern __shared__ float row[];           // [max(D, V)]
-  __shared__ float scratch[33];
   pdl_wait();
-  const int unit = blockIdx.y;
-  for (int t = blockIdx.x * a.tokens_per_block; t < min(b.n_tokens, (int)(blockIdx.x + 1) * a.tokens_per_block); ++t) {
-  __syncthreads();                                   // `row` and `scratch` are free again
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp, unit = blockIdx.y;
+  if (t >= b.n_tokens) return;
   const int s = sequence_of_token(b, t);
   const int slot = s >= 0 ? b.slot_ids[s] : -1;
-  if (slot < 0) continue;
+  if (slot < 0) return;
   const int GD = a.G * a.D, C = 2 * GD + a.H * a.V, taps = a.taps;
   const bool is_v = unit >= 2 * a.G;
   const int c0 = is_v ? 2 * GD + (unit - 2 * a.G) * a.V : unit * a.D;      // q heads, then k heads, lie back to back
@@ -60,37 +60,45 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepArgs a, IertBa
   const int pos = b.pos0[s] + (t - q_begin);
   const T* proj = (const T*)a.proj;
   float* ring = a.state + (size_t)slot * a.state_stride + a.conv_off;
+  const bool keep = t >= q_end - taps;             // the sequence's newest inputs are its history
+  float val[PREP_MAX_PER_LANE];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int c = c0 + i;
-    float acc = 0.f;
-    for (int j = taps - 1; j >= 0; --j) {          // oldest first
-      const int tj = t - j;
-      float x = 0.f;
-      if (tj >= q_begin) x = to_f32(proj[(size_t)tj * a.ld + c]);
-      else if (pos - j >= 0) x = ring[(size_t)((pos - j) % taps) * C + c];
-      acc = fmaf(a.conv_w[(size_t)c * taps + (taps - 1 - j)], x, acc);
+#pragma unroll
+  for (int k = 0; k < PREP_MAX_PER_LANE; ++k) {
+    const int i = lane + 32 * k;
+    val[k] = 0.f;
+    if (i < n) {
+      const int c = c0 + i;
+      float acc = 0.f, now = 0.f;
+      for (int j = taps - 1; j >= 0; --j) {        // oldest first
+        const int tj = t - j;
+        float x = 0.f;
+        if (tj >= q_begin) x = to_f32(proj[(size_t)tj * a.ld + c]);
+        else if (pos - j >= 0) x = ring[(size_t)((pos - j) % taps) * C + c];
+        if (j == 0) now = x;
+        acc = fmaf(a.conv_w[(size_t)c * taps + (taps - 1 - j)], x, acc);
+      }
+      val[k] = silu_f(acc);
+      ss = fmaf(val[k], val[k], ss);
+      if (keep) ring[(size_t)(pos % taps) * C + c] = now;      // a row no token of this launch reads
     }
-    const float v = silu_f(acc);
-    row[i] = v;
-    ss = fmaf(v, v, ss);
   }
-  if (t >= q_end - taps)                            // the sequence's newest inputs are its history (a pass of its
-    for (int i = threadIdx.x; i < n; i += blockDim.x)   // own, so that the loads above do not queue behind stores)
-      ring[(size_t)(pos % taps) * C + c0 + i] = to_f32(proj[(size_t)t * a.ld + c0 + i]);
   float f = 1.f;
   if (!is_v) {                                      // unit vectors; q also times dim^-1/2
-    f = 1.0f / sqrtf(block_sum(ss, scratch) + 1e-6f);
+    f = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
     if (unit < a.G) f *= 1.0f / sqrtf((float)a.D);
   }
-  for (int i = threadIdx.x; i < n; i += blockDim.x) a.qkv[(size_t)t * C + c0 + i] = row[i] * f;
+#pragma unroll
+  for (int k = 0; k < PREP_MAX_PER_LANE; ++k) {
+    const int i = lane + 32 * k;
+    if (i < n) a.qkv[(size_t)t * C + c0 + i] = val[k] * f;
+  }
   if (unit == 0)
-    for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
+    for (int h = lane; h < a.H; h += 32) {
       const float gb = a.gates[(size_t)t * a.gld + h], ga = a.gates[(size_t)t * a.gld + a.H + h];
       a.beta[(size_t)t * a.H + h] = sigmoid_f(gb);
       a.decay[(size_t)t * a.H + h] = expf(-expf(a.A_log[h]) * softplus_f(ga + a.dt_bias[h]));
     }
-  }
 }
 
 // o [T, H*V] fp32; gate: column gate_off + h*V + e of the packed projection; weight index
@@ -125,12 +133,14 @@ IERT_API int iert_delta_prep(const void* proj, int dtype, long long ld, const fl
                              int G, int D, int H, int V, int taps, const IertBatchView* batch, cudaStream_t stream) {
   if (batch->n_tokens <= 0) return IERT_OK;
   const long long C = 2LL * G * D + (long long)H * V;
-  if (G <= 0 || D <= 0 || H <= 0 || V <= 0 || taps <= 0 || D > 11000 || V > 11000 || 2 * G + H > 65535) return IERT_BAD_ARGUMENT;
+  if (G <= 0 || D <= 0 || H <= 0 || V <= 0 || taps <= 0 || D > 32 * PREP_MAX_PER_LANE || V > 32 * PREP_MAX_PER_LANE ||
+      2 * G + H > 65535)
+    return IERT_BAD_ARGUMENT;
   DeltaPrepArgs a = {proj, ld, gates, gld, conv_w, A_log, dt_bias, state, state_stride, conv_off, qkv, beta, decay,
-                     G, D, H, V, taps, batch->n_tokens >= 1024 ? 8 : 1};
+                     G, D, H, V, taps};
   (void)C;
-  const size_t smem = (size_t)(D > V ? D : V) * sizeof(float);
-  const dim3 grid((batch->n_tokens + a.tokens_per_block - 1) / a.tokens_per_block, 2 * G + H);
+  const size_t smem = 0;
+  const dim3 grid((batch->n_tokens + 3) / 4, 2 * G + H);
   if (dtype == IERT_F32) launch_dep(delta_prep_kernel<float>, grid, dim3(128), smem, stream, a, *batch);
   else if (dtype == IERT_BF16) launch_dep(delta_prep_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, a, *batch);
   else return IERT_BAD_ARGUMENT;
