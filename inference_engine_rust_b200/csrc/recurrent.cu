@@ -354,7 +354,8 @@ __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a,
 }
 
 // Lanes per column: the fewest that give the device about eight warps per SM (at most 32), and columns per
-// CTA so that a CTA has up to 256 threads.
+// CTA so that a CTA has up to 256 computing threads.  (Measured at 32 heads of 128 x 128, one prompt of 2,048
+// tokens: 8 lanes per column 1.08 ms, 16 lanes 0.91 ms, 32 lanes 1.42 ms per layer.)
 struct Split { int lanes, cols; };
 Split pick_split(int n_seqs, int H, int V) {
   const long long want = 8LL * 32 * iert_sm_count_cached();          // threads

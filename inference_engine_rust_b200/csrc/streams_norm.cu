@@ -177,7 +177,7 @@ IERT_API int iert_streams_norm(float* xs, int S, int H, float* y, const float* m
   if (S <= 0 || S > MAX_STREAMS || H <= 0 || H > 11000 || (update && (!y || !mix || !outc)) || (out && !w))
     return IERT_BAD_ARGUMENT;
   StreamsNormArgs a = {xs, S, H, y, mix, outc, update, write_back, zero_y, in_coef, w, b, eps, out, sum_out, rows_idx};
-  const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
+  const int threads = H >= 2048 ? (rows >= 512 ? 256 : 512) : H >= 512 ? 256 : 128;    // many rows: more blocks per SM
   const size_t smem = (size_t)(H + MAX_STREAMS * MAX_STREAMS + 2 * MAX_STREAMS + 33) * sizeof(float);
   if (!out || out_dtype == IERT_F32)
     launch_dep(streams_norm_kernel<float>, dim3(rows), dim3(threads), smem, stream, a);
