@@ -71,7 +71,10 @@ class VefulixConfig:
                 raise ConfigError(f"config.json: {where}.type must be one of {MIXER_TYPES}, got "
                                   f"{lr.get('type') if isinstance(lr, Mapping) else lr!r}")
             kind = lr["type"]
-            mixer = {k: _number(where + ".mixer", lr.get("mixer"), k, t) for k, t in _MIXER_KEYS[kind]}
+            given = lr.get("mixer")
+            if kind == "delta" and isinstance(given, Mapping) and given.get("kv_heads") is None and "heads" in given:
+                given = dict(given, kv_heads=given["heads"])          # no grouping given: every head has its own q and k
+            mixer = {k: _number(where + ".mixer", given, k, t) for k, t in _MIXER_KEYS[kind]}
             if kind == "delta" and mixer["heads"] % mixer["kv_heads"]:
                 raise ConfigError(f"config.json: {where}.mixer: heads {mixer['heads']} is not a multiple of "
                                   f"kv_heads {mixer['kv_heads']}")

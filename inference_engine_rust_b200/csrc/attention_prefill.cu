@@ -219,7 +219,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
   for (int r = 0; r < 2; ++r) {
     l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 1);
     l_row[r] += __shfl_xor_sync(0xffffffffu, l_row[r], 2);
-    // a sink: one more term exp(sink) in the denominator, with no key and no value
+    // a sink: a bare logit per head that adds exp(sink) to the denominator only
     if (sink && m_row[r] != -INFINITY) l_row[r] += fast_exp2(sink[head] * 1.4426950408889634f - m_row[r]);
   }
 #pragma unroll

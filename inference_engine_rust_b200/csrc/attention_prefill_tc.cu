@@ -55,7 +55,7 @@ struct PrefillTcParams {
   __nv_bfloat16* out;         // [T, heads * HD]
   int heads, kv_heads, window;
   float scale_log2e;
-  const float* sink;       // optional [heads]: one more term exp(sink) in every row's denominator (no key, no value)
+  const float* sink;       // optional [heads]: a bare logit per head that adds exp(sink) to every row's denominator only
   int* err;
 };
 

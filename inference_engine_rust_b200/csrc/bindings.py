@@ -443,7 +443,7 @@ def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, hea
     128 run on tcgen05 with the scores and the output in tensor memory (unless `legacy`); other
     multiples of 16 up to 256 run the mma.sync kernel.  The library is compiled per head size
     the first time it is needed; anything else returns False and nothing is launched.  `sink` (fp32
-    [heads], optional): one more term exp(sink) in each row's softmax denominator."""
+    [heads], optional): a bare logit per head that adds exp(sink) to each row's softmax denominator only."""
     if head_dim % 16 or not 16 <= head_dim <= 256:
         return False
     lib = _attention_lib(head_dim)

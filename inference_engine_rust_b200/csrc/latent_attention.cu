@@ -2,7 +2,8 @@
 // the cache keeps), without positions, with a sink in the softmax's denominator:
 //
 //   weights  p_j = exp(s_j - M) / (sum_j exp(s_j - M) + exp(sink_h - M)),  s_j = (q . k_j) * scale,
-//   M = max(max_j s_j, sink_h); the sink has no key and no value and is not scaled.
+//   M = max(max_j s_j, sink_h); the sink is a bare logit per head: it enters the denominator unscaled and
+//   adds nothing to the numerator.
 //
 // latent_norm_store: RMS norm (plain weight, eps inside the root) of the two down-projections of a
 //   token (query latent, key/value latent), fp32 statistics; the key/value latent is also written to

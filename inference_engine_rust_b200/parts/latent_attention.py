@@ -3,8 +3,8 @@
 Queries go through a latent: c_q = RMSnorm(W_dq h) (plain weight), q = W_uq c_q (heads x dim).  Keys and
 values come from one shared latent per token, c = RMSnorm(W_dkv h) with kv_rank numbers, the only thing
 the cache keeps: k = W_uk c, v = W_uv c per head (dim and vdim may differ).  Causal softmax of
-(q . k) * scale whose denominator also holds exp(sink_h), a learned number per head with no key and no
-value; then W_o on the concatenated heads.
+(q . k) * scale with a sink: each head has a learned logit sink_h that only enlarges the denominator by
+exp(sink_h), taken unscaled, and adds nothing to the weighted sum; then W_o on the concatenated heads.
 
 A prompt expands k and v for its own tokens and attends over them.  A one-token step attends over the
 cached latents in the absorbed form: the query is taken into the latent's coordinates (W_uk^T q), the

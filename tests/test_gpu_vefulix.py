@@ -66,12 +66,12 @@ FULL = config([layer("latent_attention", LATENT, MOE), layer("delta", DELTA, MOE
                layer("latent_attention", dict(LATENT, heads=2, dim=24, vdim=16, kv_rank=24, scale=0.35)),
                layer("delta", dict(DELTA, heads=2, kv_heads=2, dim=40, vdim=16, conv=2), MOE)],
               width=72, vocab=200, streams=2, softcap=9.0)
-# the same mechanisms at sizes the tensor-core products do not take (widths that are no multiple of 8)
+# the same mechanisms at sizes the tensor-core products and the 16-byte accesses do not take (a width of 50)
 ODD = config([layer("mlstm", dict(MLSTM, heads=3, dim=20, vdim=12), dict(MOE, router={"experts": 3, "top": 3})),
               layer("latent_attention", dict(LATENT, heads=1, dim=12, vdim=20, q_rank=12, kv_rank=20), MOE),
               layer("delta", dict(DELTA, heads=1, kv_heads=1, dim=12, vdim=12, conv=1),
                     {"kind": "moe", "expert": {"ff": 12}, "router": {"experts": 4, "top": 1}})],
-             width=52, vocab=77, streams=3, softcap=30.0, eps=1e-6)
+             width=50, vocab=77, streams=3, softcap=30.0, eps=1e-6)
 PLAIN_RESIDUAL = config([layer("delta", DELTA, MOE), layer("latent_attention", LATENT, MOE), layer("mlstm", MLSTM)],
                         width=64, vocab=128)
 
@@ -129,6 +129,9 @@ ALONE = {
     "delta_one_group": [layer("delta", dict(DELTA, heads=3, kv_heads=1, dim=32, vdim=8, conv=3))],
     "latent_attention": [layer("latent_attention", LATENT)],
     "latent_equal_sizes": [layer("latent_attention", dict(LATENT, heads=2, dim=32, vdim=32, q_rank=32, kv_rank=32))],
+    "latent_twenty_heads": [layer("latent_attention", dict(LATENT, heads=20, dim=32, vdim=32, q_rank=24, kv_rank=64, scale=0.18))],
+    "latent_forty_heads_tcgen05": [layer("latent_attention", dict(LATENT, heads=40, dim=64, vdim=64, q_rank=72, kv_rank=128, scale=0.12))],
+    "latent_rank_32": [layer("latent_attention", dict(LATENT, heads=5, dim=16, vdim=48, q_rank=16, kv_rank=32))],
     "moe": [layer("mlstm", MLSTM, MOE)],
     "moe_every_expert": [layer("mlstm", MLSTM, dict(MOE, router={"experts": 3, "top": 3}))],
     "moe_one_expert_no_shared": [layer("mlstm", MLSTM, {"kind": "moe", "expert": {"ff": 32}, "router": {"experts": 6, "top": 1}})],
