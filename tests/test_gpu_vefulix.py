@@ -309,3 +309,47 @@ def test_command_line_and_random_folder(root, capsys):
     assert cli.main(["-m", out, "-n", "5", "--stop-token", "-1", "3 9 27"]) == 0
     ids = capsys.readouterr().out.split()
     assert len([t for t in ids if t.lstrip("-").isdigit()]) >= 5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_program(root, tmp_path, dtype):
+    """bin/trace_run picks the architecture from config.json: requests whole, with their last tokens one by one,
+    and as unequal batches whose shorter requests end earlier; every wanted row against the plain implementation."""
+    from safetensors.torch import load_file, save_file
+    from inference_engine_rust_b200 import write_random_model
+    import test_gpu_trace_run as R
+    cfg = WHOLE_MODELS["full"]
+    vocab = cfg["vocab"]
+    folder = str(tmp_path / "model")
+    write_random_model(folder, cfg, seed=13, dtype=dtype, std=0.1)
+    path = os.path.join(folder, "model.safetensors")
+    tensors = load_file(path)
+    sharpen(tensors)
+    save_file({k: v.contiguous() for k, v in tensors.items()}, path)
+    weights = plain_weights(folder)
+    prompts = prompts_for({"vocab_size": vocab}, (1, 33, 64, 140), seed=2)
+    want = [P.forward(cfg, weights, p, rounding(dtype)) for p in prompts]
+
+    out = str(tmp_path / "whole")
+    R.replay(folder, dtype, R.whole_trace(prompts), out, max_tokens=192)
+    for i in range(len(prompts)):
+        compare(R.read(out, i, vocab), want[i], dtype, f"whole, request {i}")
+
+    out = str(tmp_path / "tail")
+    steps, where = R.tail_trace(prompts)
+    R.replay(folder, dtype, steps, out, max_tokens=192)
+    for i in range(len(prompts)):
+        compare(torch.cat([R.read(out, s, vocab) for s in where[i]]), want[i], dtype, f"last tokens one by one, request {i}")
+
+    out = str(tmp_path / "batch")
+    tails = {i: min(t, len(prompts[i]) - 1) for i, t in {0: 0, 1: 9, 2: 3, 3: 17}.items()}
+    steps, rows = R.batch_trace(prompts, [[3, 0, 1], [2, 1]], tails)
+    R.replay(folder, dtype, steps, out, max_tokens=320)
+    files = {}
+    for i in (0, 2, 3):
+        got = []
+        for s, r in rows[i]:
+            if s not in files:
+                files[s] = R.read(out, s, vocab)
+            got.append(files[s][r])
+        compare(torch.stack(got), want[i], dtype, f"unequal batches, request {i}")
