@@ -73,11 +73,27 @@ __global__ void __launch_bounds__(256 + LOADERS) delta_recur_kernel(DeltaArgs a,
   auto fetch = [&](int buf, int tc, int tid, int nthreads) {
     const int n = min(CHUNK, t1 - tc);
     if (DIM % 4 == 0 && C % 4 == 0 && ((uintptr_t)a.qkv & 15) == 0) {       // 16-byte loads
-      for (int x = tid; x < n * (DIM / 4); x += nthreads) {
-        const int tt = x / (DIM / 4), d = 4 * (x - tt * (DIM / 4));
-        const float* rowp = a.qkv + (size_t)(tc + tt) * C;
-        *reinterpret_cast<float4*>(&q_s[buf][tt][d]) = *reinterpret_cast<const float4*>(rowp + g * DIM + d);
-        *reinterpret_cast<float4*>(&k_s[buf][tt][d]) = *reinterpret_cast<const float4*>(rowp + GD + g * DIM + d);
+      // every load of the chunk is issued before the first is stored (a loader's loads are all it waits for)
+      constexpr int ITER = (CHUNK * (DIM / 4) + LOADERS - 1) / LOADERS;
+      float4 qv[ITER], kv[ITER];
+#pragma unroll
+      for (int it = 0; it < ITER; ++it) {
+        const int x = tid + it * nthreads;
+        if (x < n * (DIM / 4)) {
+          const int tt = x / (DIM / 4), d = 4 * (x - tt * (DIM / 4));
+          const float* rowp = a.qkv + (size_t)(tc + tt) * C;
+          qv[it] = *reinterpret_cast<const float4*>(rowp + g * DIM + d);
+          kv[it] = *reinterpret_cast<const float4*>(rowp + GD + g * DIM + d);
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < ITER; ++it) {
+        const int x = tid + it * nthreads;
+        if (x < n * (DIM / 4)) {
+          const int tt = x / (DIM / 4), d = 4 * (x - tt * (DIM / 4));
+          *reinterpret_cast<float4*>(&q_s[buf][tt][d]) = qv[it];
+          *reinterpret_cast<float4*>(&k_s[buf][tt][d]) = kv[it];
+        }
       }
     } else {
       for (int x = tid; x < n * DIM; x += nthreads) {
@@ -186,19 +202,31 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(MlstmArgs a, IertBatchV
   auto fetch = [&](int buf, int tc, int tid, int nthreads) {
     const int n = min(SCHUNK, t1 - tc);
     if (sizeof(T) == 2 && DIM % 8 == 0 && a.ld % 8 == 0 && ((uintptr_t)a.proj & 15) == 0) {      // eight bf16 per load
-      for (int x = tid; x < n * (DIM / 8) * 2; x += nthreads) {
-        const int which = x & 1, y = x >> 1;
-        const int tt = y / (DIM / 8), d = 8 * (y - tt * (DIM / 8));
-        const T* src = proj + (size_t)(tc + tt) * a.ld + (which ? a.H * DIM : 0) + head * DIM + d;
-        const uint4 v = *reinterpret_cast<const uint4*>(src);
-        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-        float* dst = which ? &k_s[buf][tt][d] : &q_s[buf][tt][d];
-        const float sc = which ? 1.f : qscale;
+      // every load of the chunk is issued before the first is converted and stored
+      constexpr int ITER = (SCHUNK * (DIM / 8) * 2 + 96 - 1) / 96;
+      uint4 raw[ITER];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(p[e]);
-          dst[2 * e] = f.x * sc;
-          dst[2 * e + 1] = f.y * sc;
+      for (int it = 0; it < ITER; ++it) {
+        const int x = tid + it * nthreads;
+        if (x < n * (DIM / 8) * 2) {
+          const int which = x & 1, y = x >> 1;
+          const int tt = y / (DIM / 8), d = 8 * (y - tt * (DIM / 8));
+          raw[it] = *reinterpret_cast<const uint4*>(proj + (size_t)(tc + tt) * a.ld + (which ? a.H * DIM : 0) + head * DIM + d);
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < ITER; ++it) {
+        const int x = tid + it * nthreads;
+        if (x < n * (DIM / 8) * 2) {
+          const int which = x & 1, y = x >> 1;
+          const int tt = y / (DIM / 8), d = 8 * (y - tt * (DIM / 8));
+          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[it]);
+          float* dst = which ? &k_s[buf][tt][d] : &q_s[buf][tt][d];
+          const float sc = which ? 1.f : qscale;
+          const float2 f0 = __bfloat1622float2(p[0]), f1 = __bfloat1622float2(p[1]);
+          const float2 f2 = __bfloat1622float2(p[2]), f3 = __bfloat1622float2(p[3]);
+          *reinterpret_cast<float4*>(dst) = make_float4(f0.x * sc, f0.y * sc, f1.x * sc, f1.y * sc);
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(f2.x * sc, f2.y * sc, f3.x * sc, f3.y * sc);
         }
       }
     } else {
@@ -281,19 +309,31 @@ __global__ void __launch_bounds__(256 + LOADERS) mlstm_recur_kernel(MlstmArgs a,
   auto fetch = [&](int buf, int tc, int tid, int nthreads) {
     const int n = min(CHUNK, t1 - tc);
     if (sizeof(T) == 2 && DIM % 8 == 0 && a.ld % 8 == 0 && ((uintptr_t)a.proj & 15) == 0) {      // eight bf16 per load
-      for (int x = tid; x < n * (DIM / 8) * 2; x += nthreads) {
-        const int which = x & 1, y = x >> 1;
-        const int tt = y / (DIM / 8), d = 8 * (y - tt * (DIM / 8));
-        const T* src = proj + (size_t)(tc + tt) * a.ld + (which ? a.H * DIM : 0) + head * DIM + d;
-        const uint4 v = *reinterpret_cast<const uint4*>(src);
-        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-        float* dst = which ? &k_s[buf][tt][d] : &q_s[buf][tt][d];
-        const float sc = which ? 1.f : qscale;
+      // every load of the chunk is issued before the first is converted and stored
+      constexpr int ITER = (CHUNK * (DIM / 8) * 2 + LOADERS - 1) / LOADERS;
+      uint4 raw[ITER];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(p[e]);
-          dst[2 * e] = f.x * sc;
-          dst[2 * e + 1] = f.y * sc;
+      for (int it = 0; it < ITER; ++it) {
+        const int x = tid + it * nthreads;
+        if (x < n * (DIM / 8) * 2) {
+          const int which = x & 1, y = x >> 1;
+          const int tt = y / (DIM / 8), d = 8 * (y - tt * (DIM / 8));
+          raw[it] = *reinterpret_cast<const uint4*>(proj + (size_t)(tc + tt) * a.ld + (which ? a.H * DIM : 0) + head * DIM + d);
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < ITER; ++it) {
+        const int x = tid + it * nthreads;
+        if (x < n * (DIM / 8) * 2) {
+          const int which = x & 1, y = x >> 1;
+          const int tt = y / (DIM / 8), d = 8 * (y - tt * (DIM / 8));
+          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw[it]);
+          float* dst = which ? &k_s[buf][tt][d] : &q_s[buf][tt][d];
+          const float sc = which ? 1.f : qscale;
+          const float2 f0 = __bfloat1622float2(p[0]), f1 = __bfloat1622float2(p[1]);
+          const float2 f2 = __bfloat1622float2(p[2]), f3 = __bfloat1622float2(p[3]);
+          *reinterpret_cast<float4*>(dst) = make_float4(f0.x * sc, f0.y * sc, f1.x * sc, f1.y * sc);
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(f2.x * sc, f2.y * sc, f3.x * sc, f3.y * sc);
         }
       }
     } else {

@@ -353,3 +353,24 @@ def test_trace_replay_program(root, tmp_path, dtype):
                 files[s] = R.read(out, s, vocab)
             got.append(files[s][r])
         compare(torch.stack(got), want[i], dtype, f"unequal batches, request {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompt_steps_replayed_as_graphs(root, dtype):
+    """Short prompt steps that want their last rows are captured into a CUDA graph from a shape bucket's
+    second use on (padding tokens and padding sequences inside): same logits as the first, eager, run, also
+    with state and pages used again in between."""
+    model, prompts, want = _setup(root, "full", dtype)
+    eng = engine_of(model, max_tokens=64 * 8, max_sequences=4)
+    batches = [[1, 0], [1, 2], [0, 1], [2, 1], [1]]                  # lengths 3, 1, 63: buckets of 16 and 64 tokens
+    for turn, batch in enumerate(batches * 2):
+        slots = [eng.open_sequence() for _ in batch]
+        got = eng.step([(s, prompts[i]) for s, i in zip(slots, batch)], want="last")
+        more = eng.step([(s, [prompts[3][len(prompts[i])]]) for s, i in zip(slots, batch)], want="last")   # and one token each
+        eng.check_device()
+        for k, i in enumerate(batch):
+            compare(got[k:k + 1], want[i][-1:], dtype, f"turn {turn}: last row of a {len(prompts[i])}-token prompt")
+        assert torch.isfinite(more).all()
+        for s in slots:
+            eng.close_sequence(s)
+    assert any(isinstance(k, tuple) and k and k[0] == "prompt" for k in eng._graphs), "no prompt step was replayed"
