@@ -20,6 +20,8 @@
 //       with i = cap tanh((zi + bi) / cap),  f = logsigmoid(cap tanh((zf + bf) / cap))
 #include "common.cuh"
 
+#include <stdlib.h>
+
 using namespace iert;
 
 #ifndef DIM
@@ -401,6 +403,10 @@ Split pick_split(int n_seqs, int H, int V) {
   const long long want = 8LL * 32 * iert_sm_count_cached();          // threads
   int lanes = R_MIN;
   while (lanes < 32 && (long long)n_seqs * H * V * lanes < want) lanes *= 2;
+  if (const char* forced = getenv("IERT_RECURRENT_LANES")) {         // for tests and measurements: 1, 2, ... 32
+    const int f = atoi(forced);
+    if (f >= 1) { lanes = R_MIN; while (lanes < 32 && lanes < f) lanes *= 2; }
+  }
   int cols = 256 / lanes;
   if (cols > V) cols = V;
   return {lanes, cols};

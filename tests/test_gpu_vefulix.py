@@ -374,3 +374,29 @@ def test_short_prompt_steps_replayed_as_graphs(root, dtype):
         for s in slots:
             eng.close_sequence(s)
     assert any(isinstance(k, tuple) and k and k[0] == "prompt" for k in eng._graphs), "no prompt step was replayed"
+
+
+@pytest.mark.parametrize("lanes", [1, 2, 8, 16])
+def test_recurrences_with_every_split_of_the_state(root, lanes, monkeypatch):
+    """The recurrent kernels keep a column of the state in 1 to 32 lanes, chosen per launch by the step's parallelism
+    (a tiny model always gets 32); forced here so that every variant is compared, in prompts and in decoding."""
+    monkeypatch.setenv("IERT_RECURRENT_LANES", str(lanes))
+    cfg = config([layer("delta", dict(DELTA, heads=2, kv_heads=1, dim=32, vdim=40, conv=3)),
+                  layer("mlstm", dict(MLSTM, heads=3, dim=24, vdim=72))], width=64, vocab=64)
+    model, weights = make_model(root, cfg, 17, "float32")
+    prompts = prompts_for({"vocab_size": cfg["vocab"]}, (70, 9, 31), seed=8)
+    eng = engine_of(model)
+    slots = [eng.open_sequence() for _ in prompts]
+    rows = [[] for _ in prompts]
+    got = eng.step([(s, p[:-5]) for s, p in zip(slots, prompts)], want="all")
+    at = 0
+    for i, p in enumerate(prompts):
+        rows[i].append(got[at:at + len(p) - 5])
+        at += len(p) - 5
+    for k in range(5, 0, -1):
+        got = eng.step([(s, [p[-k]]) for s, p in zip(slots, prompts)], want="last")
+        for i in range(len(prompts)):
+            rows[i].append(got[i:i + 1])
+    eng.check_device()
+    for i, p in enumerate(prompts):
+        compare(torch.cat(rows[i]), P.forward(cfg, weights, p), "float32", f"{lanes} lanes per column, request {i}")
