@@ -40,7 +40,9 @@ class StateRequest:
     dtype: torch.dtype = torch.float32
 
 
-CacheRequest = Union[KVRequest, StateRequest, None]
+# What a mixer asks for its layer: keys and values, a state, nothing, or a tuple of these (a mixer made of
+# several: its view is then the tuple of views, in the same order).
+CacheRequest = Union[KVRequest, StateRequest, None, Tuple]
 
 
 class KVGroup:
@@ -198,16 +200,23 @@ class Cache:
 
         kv_by_key: Dict[KVRequest, List[int]] = {}
         st_by_key: Dict[StateRequest, List[int]] = {}
+        compound: Dict[int, int] = {}          # layer -> how many requests its mixer made, if it made a tuple
         for layer in sorted(requests):
             req = requests[layer]
-            if req is None:
-                continue
-            if isinstance(req, KVRequest):
-                kv_by_key.setdefault(req, []).append(layer)
-            elif isinstance(req, StateRequest):
-                st_by_key.setdefault(req, []).append(layer)
+            if isinstance(req, (tuple, list)):
+                compound[layer] = len(req)
+                keyed = [((layer, i), r) for i, r in enumerate(req)]
             else:
-                raise TypeError(f"layer {layer}: unknown cache request {req!r}")
+                keyed = [(layer, req)]
+            for key, r in keyed:
+                if r is None:
+                    continue
+                if isinstance(r, KVRequest):
+                    kv_by_key.setdefault(r, []).append(key)
+                elif isinstance(r, StateRequest):
+                    st_by_key.setdefault(r, []).append(key)
+                else:
+                    raise TypeError(f"layer {layer}: unknown cache request {r!r}")
         self.kv_groups: List[KVGroup] = [
             KVGroup(req, layers, self.n_pages, self.n_slots, self.max_seq_len, dtype, self.device,
                     page_tokens, poison) for req, layers in kv_by_key.items()]
@@ -220,6 +229,8 @@ class Cache:
         for g in self.state_groups:
             for i, layer in enumerate(g.layers):
                 self._views[layer] = StateLayerView(g, i)
+        for layer, n in compound.items():
+            self._views[layer] = tuple(self._views.get((layer, i)) for i in range(n))
 
     def _kv_struct(self, g: KVGroup, i: int):
         if self.device.type != "cuda":

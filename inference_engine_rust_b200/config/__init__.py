@@ -5,10 +5,11 @@ from .registry import (ConfigError, architecture, architecture_name_of, config_f
 from .specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .mistral import MistralConfig  # registers "MistralForCausalLM"
 from .vefulix import VefulixConfig  # registers "Vefulix"
+from .sifasun import SifasunConfig  # registers "Sifasun"
 from .presets import PRESETS, preset
 
 __all__ = [
     "ConfigError", "architecture", "architecture_name_of", "config_from_dict",
     "known_architectures", "load_config", "read_config_json", "register_architecture",
-    "spec_of", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "MistralConfig", "VefulixConfig", "PRESETS", "preset",
+    "spec_of", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "MistralConfig", "VefulixConfig", "SifasunConfig", "PRESETS", "preset",
 ]

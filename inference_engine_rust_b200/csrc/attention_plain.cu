@@ -6,6 +6,8 @@
 //   scores  s_j = (q . k_j) * scale for j in [j_min, pos], causal by construction
 //   window  j_min = pos - (W - 1) (the last W keys, the current one included)
 //   weights softmax over the visible keys; output = sum_j p_j v_j
+//   softcap c > 0: s_j <- c tanh(s_j / c) before the softmax
+//   sink    (optional, fp32 per head): one more term exp(sink[head]) in the denominator, with no value
 // Reference: src/layers/attention.rs:364-415 (prompt), :609-645 (decode),
 // src/ops/softmax.rs:11-25; grouped heads: kv_head = head / (heads / kv_heads), :243,372.
 //
@@ -24,7 +26,8 @@ constexpr int MAX_DIMS_PER_THREAD = 4;      // head_dim up to 512
 template <typename T, bool PAGED>
 __global__ void __launch_bounds__(THREADS)
 attention_plain_kernel(const T* __restrict__ qkv, T* __restrict__ out, IertBatchView b,
-                       IertKvView c, int heads, float scale, int* __restrict__ err) {
+                       IertKvView c, int heads, float scale, float softcap, const float* __restrict__ sink,
+                       int* __restrict__ err) {
   extern __shared__ float smem[];
   const int hd = c.head_dim, nkv = c.kv_heads;
   float* q_s = smem;                  // [hd]
@@ -70,6 +73,7 @@ attention_plain_kernel(const T* __restrict__ qkv, T* __restrict__ out, IertBatch
         float dot = 0.f;
         for (int d = 0; d < hd; ++d) dot = fmaf(q_s[d], to_f32(k[d]), dot);
         sc = dot * scale;
+        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
       }
     }
     const float m_new = fmaxf(m, block_max(sc, scratch));
@@ -103,6 +107,7 @@ attention_plain_kernel(const T* __restrict__ qkv, T* __restrict__ out, IertBatch
     }
     __syncthreads();
   }
+  if (sink) l += expf(sink[head] - m);
   const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < MAX_DIMS_PER_THREAD; ++i) {
@@ -118,7 +123,7 @@ attention_plain_kernel(const T* __restrict__ qkv, T* __restrict__ out, IertBatch
 // step must start at position 0); paged = 1 reads them from the cache view.
 IERT_API int iert_attention_plain(const void* qkv, void* out, int dtype, const IertBatchView* batch,
                                   const IertKvView* cache, int heads, float scale, int paged,
-                                  int* err, cudaStream_t stream) {
+                                  float softcap, const float* sink, int* err, cudaStream_t stream) {
   if (batch->n_tokens <= 0) return IERT_OK;
   const int hd = cache->head_dim;
   if (hd <= 0 || hd > THREADS * MAX_DIMS_PER_THREAD || heads <= 0 || cache->kv_heads <= 0 ||
@@ -128,7 +133,7 @@ IERT_API int iert_attention_plain(const void* qkv, void* out, int dtype, const I
   dim3 grid(batch->n_tokens, heads);
   const size_t smem = (size_t)(hd + THREADS + 33) * sizeof(float);
 #define GO(T, P) attention_plain_kernel<T, P><<<grid, THREADS, smem, stream>>>( \
-    (const T*)qkv, (T*)out, *batch, *cache, heads, scale, err)
+    (const T*)qkv, (T*)out, *batch, *cache, heads, scale, softcap, sink, err)
   if (dtype == IERT_F32) { if (paged) GO(float, true); else GO(float, false); }
   else if (dtype == IERT_BF16) { if (paged) GO(__nv_bfloat16, true); else GO(__nv_bfloat16, false); }
   else return IERT_BAD_ARGUMENT;

@@ -98,7 +98,7 @@ def _declare(lib) -> None:
         "iert_add_into": [P, P, c_int, c_longlong, S],
         "iert_advance_positions": [P, P, P, c_int, S],
         "iert_gemm_plain": [P, c_int, P, c_int, P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, S],
-        "iert_attention_plain": [P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_float, c_int, P, S],
+        "iert_attention_plain": [P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_float, c_int, c_float, P, P, S],
         "iert_sample_greedy": [P, c_int, c_int, c_longlong, P, P, S],
         "iert_sample_temperature": [P, c_int, c_int, c_longlong, c_float, c_ulonglong, P, P, P, P, S],
         "iert_uniform_draws": [c_ulonglong, P, P, P, c_int, S],
@@ -121,6 +121,14 @@ def _declare(lib) -> None:
         "iert_latent_decode_tc_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)],
         "iert_router_topk": [P, LL, P, c_int, c_int, c_int, P, P, P, S],
         "iert_moe_scale": [P, c_int, LL, P, c_int, c_int, c_int, S],
+        "iert_add_normed": [P, P, P, P, c_int, c_int, c_int, c_float, S],
+        "iert_cast_rows": [P, P, P, c_int, LL, S],
+        "iert_scale_values": [P, LL, c_float, S],
+        "iert_qk_prep": [P, LL, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, P, c_int, c_int, P, P, c_float, c_float,
+                         c_int, P, S],
+        "iert_rglru_conv": [P, LL, P, P, P, P, LL, P, c_int, c_int, POINTER(BatchView), S],
+        "iert_rglru_gates": [P, P, P, P, P, c_int, P, c_float, P, P, c_int, c_int, c_int, S],
+        "iert_rglru_scan": [P, P, P, LL, P, P, P, LL, P, c_int, c_float, c_int, c_int, POINTER(BatchView), S],
     })
     lib.iert_attention_decode.argtypes = [P, P, POINTER(BatchView), POINTER(KvView), c_int, c_float, c_int, P, P, S]
     lib.iert_attention_decode.restype = c_int
@@ -270,9 +278,12 @@ def gemm_plain(x, w, out, M: int, mode: int, stream) -> None:
 
 
 def attention_plain(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: float, paged: bool,
-                    err, stream) -> None:
+                    err, stream, softcap: float = 0.0, sink=None) -> None:
+    """`softcap` c > 0: scores pass c tanh(s / c); `sink` (fp32 [heads], optional): a bare logit per head
+    that adds exp(sink) to each row's softmax denominator only."""
     check(core().iert_attention_plain(qkv.data_ptr(), out.data_ptr(), dtype_code(qkv.dtype),
                                       byref(batch), byref(kv), heads, scale, 1 if paged else 0,
+                                      softcap, sink.data_ptr() if sink is not None else None,
                                       err.data_ptr(), stream), "attention_plain")
 
 
@@ -688,3 +699,54 @@ def router_topk(z, bias, n_tokens: int, E: int, top: int, wt, idx, w, stream) ->
 def moe_scale(act, wt, n_tokens: int, E: int, F: int, stream) -> None:
     check(core().iert_moe_scale(act.data_ptr(), dtype_code(act.dtype), act.stride(0), wt.data_ptr(), n_tokens, E, F, stream),
           "moe_scale")
+
+
+# ---------------------------------------------------------------------------------------
+# norm on a sublayer's output, keys that double as values, the gated linear recurrence
+
+
+def add_normed(x, y, w, cast, rows: int, eps: float, stream) -> None:
+    """x[:rows] += y / rms(y) * w (fp32; w with any offset already added); y's rows are cleared; `cast`
+    (optional) receives the new rows in its dtype."""
+    check(core().iert_add_normed(x.data_ptr(), y.data_ptr(), w.data_ptr(), _ptr(cast),
+                                 dtype_code(cast.dtype) if cast is not None else F32, rows, x.shape[-1], eps, stream),
+          "add_normed")
+
+
+def cast_rows(x, y, cast, rows: int, stream) -> None:
+    """cast[:rows] = x[:rows] in cast's dtype; y[:rows] = 0 (y optional)."""
+    check(core().iert_cast_rows(x.data_ptr(), _ptr(y), cast.data_ptr(), dtype_code(cast.dtype), rows * x.shape[-1], stream),
+          "cast_rows")
+
+
+def scale_values(z, s: float, stream) -> None:
+    check(core().iert_scale_values(z.data_ptr(), z.numel(), s, stream), "scale_values")
+
+
+NORM_NONE, NORM_WHOLE_WEIGHTED, NORM_HEAD_UNIT = 0, 1, 2
+
+
+def qk_prep(proj, qkv, batch: BatchView, kv: KvView, heads: int, inv_freq, rotary_dim: int, norm_mode: int, wq, wk,
+            eps: float, value_scale: float, store: bool, err, stream) -> None:
+    """From the fp32 projection rows [q | k] to the packed rows [q' | k' | v] (v = k as projected times
+    `value_scale`), with the norm of `norm_mode`, the rotation, and the cache write of k' and v."""
+    check(core().iert_qk_prep(proj.data_ptr(), proj.stride(0), qkv.data_ptr(), dtype_code(qkv.dtype), byref(batch), byref(kv),
+                              heads, inv_freq.data_ptr(), rotary_dim, norm_mode, _ptr(wq), _ptr(wk), eps, value_scale,
+                              1 if store else 0, err.data_ptr(), stream), "qk_prep")
+
+
+def rglru_conv(proj, bx, taps, cb, state, u, C: int, K: int, batch: BatchView, stream) -> None:
+    check(core().iert_rglru_conv(proj.data_ptr(), proj.stride(0), bx.data_ptr(), taps.data_ptr(), cb.data_ptr(),
+                                 state.data_ptr(), state.stride(0), u.data_ptr(), C, K, byref(batch), stream), "rglru_conv")
+
+
+def rglru_gates(u, ra, ra_b, ri, ri_b, lam, decay_c: float, A, Bv, n_tokens: int, C: int, blocks: int, stream) -> None:
+    check(core().iert_rglru_gates(u.data_ptr(), ra.data_ptr(), ra_b.data_ptr(), ri.data_ptr(), ri_b.data_ptr(),
+                                  dtype_code(ra.dtype), lam.data_ptr(), decay_c, A.data_ptr(), Bv.data_ptr(), n_tokens, C,
+                                  blocks, stream), "rglru_gates")
+
+
+def rglru_scan(A, Bv, proj, by, bx, state, out, out_scale: float, C: int, K: int, batch: BatchView, stream) -> None:
+    check(core().iert_rglru_scan(A.data_ptr(), Bv.data_ptr(), proj.data_ptr(), proj.stride(0), by.data_ptr(), bx.data_ptr(),
+                                 state.data_ptr(), state.stride(0), out.data_ptr(), dtype_code(out.dtype), out_scale, C, K,
+                                 byref(batch), stream), "rglru_scan")

@@ -1,0 +1,137 @@
+// Preparation of queries and keys for attention whose keys double as values: from the fp32 projection
+// row [q | k] of a token to the packed row [q' | k' | v] that the attention kernels read, plus the cache
+// write of k' and v.  All arithmetic fp32, one rounding at the end.
+//
+//   v  = k as projected, times `value_scale` (a fixed factor on the mixer's result, which is linear in v)
+//   norm_mode 1: q and k each divided by the root mean square over their WHOLE projection and multiplied
+//                by a weight of that length, before the rotation
+//   rotation of the first `rotary_dim` numbers of every head, number i with number i + rotary_dim / 2,
+//                by position * inv_freq[i]
+//   norm_mode 2: after the rotation every head of q and k divided by its own root mean square (no weight)
+//
+// One block per token.  The row is held in shared memory.
+#include "common.cuh"
+
+using namespace iert;
+
+namespace {
+
+constexpr int THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+qk_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ qkv, IertBatchView b, IertKvView c, int heads,
+               const float* __restrict__ inv_freq, int rotary_dim, int norm_mode, const float* __restrict__ wq,
+               const float* __restrict__ wk, float eps, float value_scale, int write_cache, int* __restrict__ err) {
+  extern __shared__ float sm[];
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  const int hd = c.head_dim, nkv = c.kv_heads;
+  const int qd = heads * hd, kd = nkv * hd, half = rotary_dim / 2;
+  float* row = sm;                       // [qd + kd]
+  float* cs = sm + qd + kd;              // [half] cos, [half] sin
+  const int t = blockIdx.x;
+  const int s = sequence_of_token(b, t);
+  const int slot = s < 0 ? -1 : b.slot_ids[s];
+  if (slot < 0) return;
+  const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
+  const int pos = b.pos0[s] + (t - q_begin);
+  const int final_len = b.pos0[s] + q_len;
+  for (int k = threadIdx.x; k < half; k += THREADS) {
+    float sn, co;
+    sincosf((float)pos * inv_freq[k], &sn, &co);
+    cs[k] = co;
+    cs[half + k] = sn;
+  }
+  pdl_wait();
+  const bool store = write_cache && pos >= final_len - c.ring_pages * c.page_tokens;
+  const float* pr = proj + (size_t)t * ld;
+  T* out = qkv + (size_t)t * (qd + 2 * kd);
+  float ssq = 0.f, ssk = 0.f;
+  for (int i = threadIdx.x; i < qd + kd; i += THREADS) {
+    const float v = pr[i];
+    row[i] = v;
+    if (i < qd) ssq = fmaf(v, v, ssq); else ssk = fmaf(v, v, ssk);
+  }
+  if (norm_mode == 1) {
+    ssq = block_sum(ssq, scratch);
+    ssk = block_sum(ssk, scratch);
+  } else {
+    __syncthreads();
+  }
+  // the values: the keys as projected
+  for (int i = threadIdx.x; i < kd; i += THREADS) {
+    const T v = from_f32<T>(row[qd + i] * value_scale);
+    out[qd + kd + i] = v;
+    if (store) {
+      const int h = i / hd, d = i - h * hd;
+      const long long off = kv_row_offset(c, slot, pos, h, err);
+      if (off >= 0) ((T*)c.v)[off + d] = v;
+    }
+  }
+  if (norm_mode == 1) {
+    const float rq = 1.0f / sqrtf(ssq / (float)qd + eps), rk = 1.0f / sqrtf(ssk / (float)kd + eps);
+    __syncthreads();
+    for (int i = threadIdx.x; i < qd + kd; i += THREADS)
+      row[i] = i < qd ? row[i] * rq * wq[i] : row[i] * rk * wk[i - qd];
+  }
+  __syncthreads();
+  // rotation: one thread per pair
+  const int n_heads = heads + nkv;
+  for (int i = threadIdx.x; i < n_heads * half; i += THREADS) {
+    const int h = i / half, k = i - h * half;
+    float* v = row + (size_t)h * hd;
+    const float a = v[k], bb = v[k + half];
+    v[k] = a * cs[k] - bb * cs[half + k];
+    v[k + half] = bb * cs[k] + a * cs[half + k];
+  }
+  __syncthreads();
+  if (norm_mode == 2) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int h = warp; h < n_heads; h += THREADS / 32) {
+      float* v = row + (size_t)h * hd;
+      float ss = 0.f;
+      for (int d = lane; d < hd; d += 32) ss = fmaf(v[d], v[d], ss);
+      ss = warp_sum(ss);
+      const float r = 1.0f / sqrtf(ss / (float)hd + eps);
+      for (int d = lane; d < hd; d += 32) v[d] *= r;
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < qd + kd; i += THREADS) {
+    const T v = from_f32<T>(row[i]);
+    out[i] = v;
+    if (store && i >= qd) {
+      const int j = i - qd, h = j / hd, d = j - h * hd;
+      const long long off = kv_row_offset(c, slot, pos, h, nullptr);
+      if (off >= 0) ((T*)c.k)[off + d] = v;
+    }
+  }
+}
+
+}  // namespace
+
+// proj: fp32 [T, heads*hd + kv_heads*hd] (row stride ld); qkv: [T, (heads + 2 kv_heads) * hd] of `dtype` (= the cache's).
+IERT_API int iert_qk_prep(const float* proj, long long ld, void* qkv, int dtype, const IertBatchView* batch,
+                          const IertKvView* cache, int heads, const float* inv_freq, int rotary_dim, int norm_mode,
+                          const float* wq, const float* wk, float eps, float value_scale, int write_cache, int* err,
+                          cudaStream_t stream) {
+  if (batch->n_tokens <= 0) return IERT_OK;
+  const int hd = cache->head_dim;
+  if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1) || cache->dtype != dtype || norm_mode < 0 || norm_mode > 2 ||
+      (norm_mode == 1 && (!wq || !wk)))
+    return IERT_BAD_ARGUMENT;
+  const size_t smem = ((size_t)(heads + cache->kv_heads) * hd + rotary_dim) * sizeof(float);
+  if (smem > 200 * 1024) return IERT_BAD_ARGUMENT;
+#define GO(T)                                                                                                          \
+  do {                                                                                                                 \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(qk_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    launch_dep(qk_prep_kernel<T>, dim3(batch->n_tokens), dim3(THREADS), smem, stream, proj, ld, (T*)qkv, *batch, *cache,    \
+               heads, inv_freq, rotary_dim, norm_mode, wq, wk, eps, value_scale, write_cache, err);                      \
+  } while (0)
+  if (dtype == IERT_F32) GO(float);
+  else if (dtype == IERT_BF16) GO(__nv_bfloat16);
+  else return IERT_BAD_ARGUMENT;
+#undef GO
+  return iert_check_launch("qk_prep");
+}

@@ -1,12 +1,14 @@
 """The parts layers are assembled from.  Importing this package registers the built-in
 kinds: norm "rmsnorm", position "rope", mixer "attention", ffn "swiglu", block "prenorm",
 head "linear"; norm "layernorm", block "hyper" (a residual of several streams), input "embed_norm",
-head "softcap", ffn "moe", mixers "mlstm", "gated_delta" and "latent_attention"."""
+head "softcap", ffn "moe", mixers "mlstm", "gated_delta" and "latent_attention"; block "outnorm" (the norm on a
+sublayer's output), head "scaled", mixers "tied_kv_attention" (keys double as values), "rglru" (a gated linear
+recurrence with a short convolution) and "parallel" (two mixers side by side)."""
 from .base import (Block, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, Runtime, StepContext, StepInput,
                    Workspace, part_class, register_part, unregister_part)
 from .linear import Linear
 from . import (norm, rope, attention, swiglu, block, head, inputs, moe, recurrent,  # noqa: F401  (registration)
-               latent_attention)
+               latent_attention, tied_attention, rglru, parallel)
 
 __all__ = ["Block", "FeedForward", "Head", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime",
            "StepContext", "StepInput", "Workspace", "part_class", "register_part", "unregister_part", "Linear"]

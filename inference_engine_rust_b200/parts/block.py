@@ -125,5 +125,46 @@ class HyperConnectionBlock(Block):
             B.streams_norm(xs, S, H, T, ctx.stream, y=y, mix=update[1], outc=update[2], update=True, write_back=True)
 
 
+class CastAhead:
+    """Left in `ctx.rows_ahead` by an output-norm block: the residual rows `rows` already stand in `cast` in the
+    run's dtype and the sublayer buffer `cleared` is zero, written by the kernel that finished the block."""
+
+    def __init__(self, rows, cast, cleared):
+        self.rows, self.cast, self.cleared = rows, cast, cleared
+
+
+class OutputNormBlock(Block):
+    """The norm sits on each sublayer's OUTPUT and the sublayers read the residual itself:
+
+        x <- x + norm1(mixer(x));   x <- x + norm2(ffn(x))      (the second half left out without a feed-forward)
+
+    The sublayers add into a zeroed fp32 buffer y; one kernel per sublayer norms y, adds it to the fp32 residual,
+    clears y and writes the new residual in the run's dtype for the next sublayer's projections (also across the
+    block boundary: the next block of this kind finds its input ready)."""
+    graph_safe = True
+
+    def __init__(self, layer_spec, norm1, mixer, norm2, ffn, rt: Runtime):
+        self.norm1, self.mixer, self.norm2, self.ffn, self.rt = norm1, mixer, norm2, ffn, rt
+        for n in (norm1, norm2):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ValueError(f"block 'outnorm' needs a norm with add_normed, got {type(n).__name__}")
+
+    def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool) -> None:
+        rt, T = self.rt, ctx.n_tokens
+        ctx.norm_ahead = None
+        y = rt.workspace.take("block.sublayer_out", x.shape, torch.float32)
+        h = rt.workspace.take("block.input", x.shape, rt.dtype)
+        ahead, ctx.rows_ahead = ctx.rows_ahead, None
+        if not (isinstance(ahead, CastAhead) and ahead.rows is x and ahead.cast is h and ahead.cleared is y):
+            B.cast_rows(x, y, h, T, ctx.stream)
+        self.mixer.forward(h, y, ctx, cache_view, writes_cache)
+        self.norm1.add_normed(y, x, h, ctx, T)
+        if self.ffn is not None:
+            self.ffn.forward(h, y, ctx)
+            self.norm2.add_normed(y, x, h, ctx, T)
+        ctx.rows_ahead = CastAhead(x, h, y)
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "outnorm", OutputNormBlock)
 register_part("block", "hyper", HyperConnectionBlock)

@@ -96,6 +96,9 @@ def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:
     rt = attn.rt
     if qkv.dtype != torch.bfloat16:
         return False
+    softcap, sink = getattr(attn, "softcap", 0.0), getattr(attn, "sink", None)
+    if softcap or sink is not None:
+        return False
     if ctx.kind == "decode":
         splits = decode_splits(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads, attn.head_dim)
         parts, target = decode_parts(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads, ctx.unequal_lengths, attn.head_dim)

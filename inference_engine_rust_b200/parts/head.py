@@ -54,5 +54,20 @@ class SoftCapHead(LinearHead):
         B.softcap(logits[:n_rows], self.cap, ctx.stream)
 
 
+class ScaledHead(LinearHead):
+    """logits <- logits * scale after the product (spec: "scale")."""
+
+    def __init__(self, spec: PartSpec, hidden_size: int, vocab_size: int, rt: Runtime):
+        super().__init__(spec, hidden_size, vocab_size, rt)
+        self.scale = float(spec["scale"])
+
+    def forward(self, hn, logits, n_rows: int, ctx: StepContext) -> None:
+        from ..csrc import bindings as B
+        super().forward(hn, logits, n_rows, ctx)
+        if self.scale != 1.0:
+            B.scale_values(logits[:n_rows], self.scale, ctx.stream)
+
+
 register_part("head", "linear", LinearHead)
+register_part("head", "scaled", ScaledHead)
 register_part("head", "softcap", SoftCapHead)

@@ -1,5 +1,6 @@
 """RMSNorm: out = x * w / sqrt(mean(x^2) + eps), eps inside the root, the scale multiplies
-plainly (src/ops/rmsnorm.rs:38-48).  Statistics in fp32 on the fp32 residual stream."""
+plainly (src/ops/rmsnorm.rs:38-48).  Statistics in fp32 on the fp32 residual stream.  With the spec's
+`offset` c the stored weight lies around zero and the scale is c + w (formed once, in fp32)."""
 from __future__ import annotations
 
 from typing import Dict, Mapping
@@ -47,15 +48,23 @@ class RMSNorm(Norm):
 
     def __init__(self, spec, hidden_size: int, rt: Runtime):
         self.eps = float(spec["eps"])
+        self.offset = float(spec.get("offset", 0.0))
         self.hidden_size = hidden_size
         self.rt = rt
         self.weight = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.hidden_size,), "ones_plus_normal")}
+        return {"weight": TensorSpec((self.hidden_size,), "normal" if self.offset else "ones_plus_normal")}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        w = tensors["weight"]
+        self.weight = (w.to(torch.float32) + self.offset).contiguous() if self.offset else w.contiguous()
+        self._weight_f32 = self.weight if self.weight.dtype == torch.float32 else self.weight.to(torch.float32)
+
+    def add_normed(self, y, x, cast, ctx, rows: int) -> None:
+        """x[:rows] += norm(y[:rows]) for a layer that norms a sublayer's output (fp32 both); clears y's rows
+        for the sublayer to come and writes the new rows into `cast` (the run's dtype, optional)."""
+        B.add_normed(x, y, self._weight_f32, cast, rows, self.eps, ctx.stream)
 
     def forward(self, x, out, ctx, rows_idx=None, rows=None) -> None:
         B.rmsnorm(x, self.weight, out, self.eps, ctx.stream, rows_idx=rows_idx, rows=rows)

@@ -22,22 +22,22 @@ class SwiGLU(FeedForward):
         self.rt = rt
         self.hidden_size = int(spec["hidden_size"])
         self.intermediate_size = int(spec["intermediate_size"])
+        # local tensor names of (gate, up, down); an architecture whose files name them otherwise says so
+        self.names = tuple(spec.get("tensor_names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
         self.gate_up = None
         self.down = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         h, i = self.hidden_size, self.intermediate_size
-        return {
-            "gate_proj.weight": TensorSpec((i, h)),
-            "up_proj.weight": TensorSpec((i, h)),
-            "down_proj.weight": TensorSpec((h, i)),
-        }
+        gate, up, down = self.names
+        return {gate: TensorSpec((i, h)), up: TensorSpec((i, h)), down: TensorSpec((h, i))}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         dt = self.rt.dtype
-        fused = torch.cat([tensors["gate_proj.weight"].to(dt), tensors["up_proj.weight"].to(dt)], dim=0)
+        gate, up, down = self.names
+        fused = torch.cat([tensors[gate].to(dt), tensors[up].to(dt)], dim=0)
         self.gate_up = Linear(fused, self.rt)
-        self.down = Linear(tensors["down_proj.weight"], self.rt)
+        self.down = Linear(tensors[down], self.rt)
 
     def weight_bytes(self) -> int:
         return self.gate_up.nbytes() + self.down.nbytes()
