@@ -55,6 +55,31 @@ PRESETS["vefulix-7b-sizes"] = _vefulix(4096, 32000, 32, 2, 32, 128, 128, 1536, 5
 PRESETS["vefulix-tiny"] = _vefulix(96, 320, 4, 2, 4, 16, 24, 48, 40, 6, 2, 32, 64)
 
 
+def _sifasun(width, vocab, layers, heads, kv_heads, dim, ff, lru_width, blocks, window, shared_from=None):
+    """A Sifasun configuration: one pair layer (attention beside a gated linear recurrence), then three attention
+    layers, round and round; from layer `shared_from` on, layers run with the weights of the layer that many places
+    before them."""
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+                 "mask": {"size": window}, "rot": {"base": 500000.0, "dims": dim // 2, "scaling": {"factor": 4.0}}}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+            "mask": {"size": 2 * window}, "rot": {"base": 250000.0, "dims": dim}}
+    pair = {"left": left, "left_scale": 1.1, "right": {"width": lru_width, "blocks": blocks, "conv": 4}, "right_scale": 0.9}
+    out = []
+    for i in range(layers):
+        entry = {"type": "parallel" if i % 4 == 0 else "attention", "mixer": dict(pair if i % 4 == 0 else attention),
+                 "mlp": {"kind": "dense", "ff": ff}}
+        if shared_from is not None and i >= shared_from:
+            entry["weights_of"] = i - shared_from
+        out.append(entry)
+    return {"architecture": "Sifasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": out}
+
+
+# Sifasun at the width, head count, head size and feed-forward size of Mistral 7B (a recurrence as wide as the model in
+# 16 blocks), and a tiny one that runs anywhere in seconds (its last four layers run with the first four's weights).
+PRESETS["sifasun-7b-sizes"] = _sifasun(4096, 32000, 32, 32, 8, 128, 14336, 4096, 16, 2048)
+PRESETS["sifasun-tiny"] = _sifasun(96, 320, 8, 4, 2, 16, 160, 64, 4, 24, shared_from=4)
+
+
 def preset(name: str) -> dict:
     """A copy of the named configuration (a config.json-style dict)."""
     try:

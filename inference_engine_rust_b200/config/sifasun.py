@@ -56,9 +56,9 @@ def _attention(where: str, raw: Any) -> Dict[str, Any]:
     rot = raw.get("rot")
     out = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": _number(where, raw, "scale", float)}
     if rot is not None:
-        dims = _number(where + ".rot", rot, "dims", int)
-        if dims % 2 or dims > dim:
-            raise ConfigError(f"config.json: {where}.rot.dims {dims} must be even and at most dim {dim}")
+        dims = _number(where + ".rot", rot, "dims", int, positive=False)
+        if dims < 0 or dims % 2 or dims > dim:
+            raise ConfigError(f"config.json: {where}.rot.dims {dims} must be even, not negative and at most dim {dim}")
         out["rot"] = {"base": _number(where + ".rot", rot, "base", float), "dims": dims}
         if rot.get("scaling") is not None:
             out["rot"]["scaling"] = {"factor": _number(where + ".rot.scaling", rot["scaling"], "factor", float)}

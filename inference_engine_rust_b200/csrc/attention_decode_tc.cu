@@ -51,6 +51,8 @@ struct DecodeTcParams {
   int heads, splits, slices, gt;
   int target_ctas;            // > 0: a sequence is cut into as many of the `splits` parts as its length asks for
   float scale_log2e;
+  float cap_k2, cap_l2e;      // a soft cap on the scores (cap_l2e > 0): see softcap_l2
+  const float* sink;          // optional [heads]: a bare logit per head that adds exp(sink) to the denominator only
   int* err;
   // Fused position encoding (rope != 0): `qkv` comes straight from the projection; the kernel
   // rotates the queries and the new key itself and, if store != 0, writes the new key and
@@ -316,7 +318,7 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int j = jbase + n * 8 + tq * 2 + e;
-        v[n][e] = (j >= j_min && j <= pos) ? sc[n][e] * p.scale_log2e : -INFINITY;
+        v[n][e] = (j >= j_min && j <= pos) ? (p.cap_l2e > 0.f ? softcap_l2(sc[n][e], p.cap_k2, p.cap_l2e) : sc[n][e] * p.scale_log2e) : -INFINITY;
         mx = fmaxf(mx, v[n][e]);
       }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -370,6 +372,7 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
       wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - mm);
       ll += wgt[w] * ml_s[(w * 8 + r) * 2 + 1];
     }
+    if (direct && p.sink && mm != -INFINITY) ll += exp2f(p.sink[head0 + r] * 1.4426950408889634f - mm);
     const float inv = ll > 0.f ? 1.0f / ll : 0.f;
     for (int d = threadIdx.x; d < HD; d += THREADS) {
       float acc = 0.f;
@@ -643,7 +646,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int j = jbase + n * 8 + tq * 2 + e;
-        v[n][e] = (j >= j_min && j <= pos) ? sc[n][e] * p.scale_log2e : -INFINITY;
+        v[n][e] = (j >= j_min && j <= pos) ? (p.cap_l2e > 0.f ? softcap_l2(sc[n][e], p.cap_k2, p.cap_l2e) : sc[n][e] * p.scale_log2e) : -INFINITY;
         mx = fmaxf(mx, v[n][e]);
       }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -720,6 +723,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - mm);
       ll += wgt[w] * ml_s[(w * 8 + r) * 2 + 1];
     }
+    if (direct && p.sink && mm != -INFINITY) ll += exp2f(p.sink[head0 + r] * 1.4426950408889634f - mm);
     const float inv = ll > 0.f ? 1.0f / ll : 0.f;
     for (int d = threadIdx.x; d < HD; d += THREADS) {
       float acc = 0.f;
@@ -760,6 +764,7 @@ __global__ void attention_decode_tc_combine_kernel(DecodeTcParams p, IertBatchVi
   for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, pml[2 * s]);
   float ll = 0.f;
   for (int s = 0; s < n_splits; ++s) ll += pml[2 * s] == -INFINITY ? 0.f : exp2f(pml[2 * s] - mm) * pml[2 * s + 1];
+  if (p.sink && mm != -INFINITY) ll += exp2f(p.sink[head] * 1.4426950408889634f - mm);
   const float inv = ll > 0.f ? 1.0f / ll : 0.f;
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float acc = 0.f;
@@ -785,7 +790,7 @@ namespace {
 
 int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const IertKvView* cache, int heads,
                   float scale, int splits, int target_ctas, float* scratch, const float* inv_freq, int rope, int rotary_dim,
-                  int pairing, int store, int* err, cudaStream_t stream) {
+                  int pairing, int store, float softcap, const float* sink, int* err, cudaStream_t stream) {
   const int T = batch->n_tokens;
   if (T <= 0) return IERT_OK;
   if (cache->dtype != IERT_BF16 || cache->head_dim != HD || cache->page_tokens != PAGE || splits < 1 || heads <= 0 ||
@@ -802,6 +807,9 @@ int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const 
   p.gt = group < 8 ? group : 8;                      // heads per CTA (rows 0..7 of the MMA tile)
   p.slices = (group + p.gt - 1) / p.gt;
   p.scale_log2e = scale * 1.4426950408889634f;
+  p.cap_k2 = softcap > 0.f ? 2.0f * scale * 1.4426950408889634f / softcap : 0.f;
+  p.cap_l2e = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.sink = sink;
   p.err = err;
   p.part_out = scratch;
   p.part_ml = scratch + (size_t)T * heads * splits * HD;
@@ -860,9 +868,10 @@ int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const 
 // HEAD_DIM, bf16, 64-position pages.  Anything else: IERT_BAD_ARGUMENT, nothing launched.
 IERT_API int iert_attention_decode_tc(const void* qkv, void* out, const IertBatchView* batch,
                                       const IertKvView* cache, int heads, float scale, int splits,
-                                      int target_ctas, float* scratch, int* err, cudaStream_t stream) {
-  return launch_decode(qkv, out, batch, cache, heads, scale, splits, target_ctas, scratch, nullptr, 0, 0, 0, 0, err,
-                       stream);
+                                      int target_ctas, float* scratch, float softcap, const float* sink, int* err,
+                                      cudaStream_t stream) {
+  return launch_decode(qkv, out, batch, cache, heads, scale, splits, target_ctas, scratch, nullptr, 0, 0, 0, 0, softcap,
+                       sink, err, stream);
 }
 
 // The same with the rotary encoding and the cache write of the step inside the kernel: `qkv` is
@@ -875,5 +884,5 @@ IERT_API int iert_attention_decode_tc_rope(const void* qkv, void* out, const Ier
                                            int pairing, int store, int* err, cudaStream_t stream) {
   if (batch->n_tokens != batch->n_seqs) return IERT_BAD_ARGUMENT;     // one token per sequence
   return launch_decode(qkv, out, batch, cache, heads, scale, splits, target_ctas, scratch, inv_freq, 1, rotary_dim,
-                       pairing, store, err, stream);
+                       pairing, store, 0.f, nullptr, err, stream);
 }

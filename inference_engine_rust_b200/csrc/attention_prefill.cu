@@ -80,7 +80,7 @@ __device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* sr
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out,
                          IertBatchView b, int heads, int kv_heads, int window, float scale_log2e,
-                         const float* __restrict__ sink) {
+                         const float* __restrict__ sink, float cap_k2, float cap_l2e) {
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* q_tile = smem;
   auto k_tile = [&](int i) { return smem + Q_TILE_BYTES + i * TILE_BYTES; };
@@ -163,7 +163,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
     for (int n = 0; n < BN / 8; ++n) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float v = sc[n][e] * scale_log2e;
+        float v = cap_l2e > 0.f ? softcap_l2(sc[n][e], cap_k2, cap_l2e) : sc[n][e] * scale_log2e;
         if (need_mask) {
           const int j = j0 + n * 8 + tq * 2 + (e & 1), i = qi[e >> 1];
           const bool vis = j <= i && j < len && (window <= 0 || j >= i - (window - 1));
@@ -243,7 +243,7 @@ IERT_API int iert_attention_prefill_head_dim() { return HD; }
 // max_q_len: the longest sequence of the step (sizes the grid).
 IERT_API int iert_attention_prefill(const void* qkv, void* out, const IertBatchView* batch, int heads,
                                     int kv_heads, int window, float scale, int max_q_len, const float* sink,
-                                    cudaStream_t stream) {
+                                    float softcap, cudaStream_t stream) {
   if (batch->n_tokens <= 0 || max_q_len <= 0) return IERT_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || batch->n_seqs > 65535)
     return IERT_BAD_ARGUMENT;
@@ -259,7 +259,8 @@ IERT_API int iert_attention_prefill(const void* qkv, void* out, const IertBatchV
   dim3 grid((max_q_len + BM - 1) / BM, heads, batch->n_seqs);
   attention_prefill_kernel<<<grid, THREADS, smem, stream>>>(
       (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, *batch, heads, kv_heads, window,
-      scale * 1.4426950408889634f, sink);
+      scale * 1.4426950408889634f, sink, softcap > 0.f ? 2.0f * scale * 1.4426950408889634f / softcap : 0.f,
+      softcap > 0.f ? softcap * 1.4426950408889634f : 0.f);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
 }

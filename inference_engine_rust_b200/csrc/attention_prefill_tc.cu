@@ -55,6 +55,7 @@ struct PrefillTcParams {
   __nv_bfloat16* out;         // [T, heads * HD]
   int heads, kv_heads, window;
   float scale_log2e;
+  float cap_k2, cap_l2e;   // a soft cap on the scores (cap_l2e > 0): see softcap_l2
   const float* sink;       // optional [heads]: a bare logit per head that adds exp(sink) to every row's denominator only
   int* err;
 };
@@ -247,6 +248,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int c = 0; c < BN; ++c) sc[c] = __uint_as_float(raw[c]);
       }
+      // With a soft cap the scores are capped here, in base-2 units, and the scale below is 1.
+      const float sl2 = p.cap_l2e > 0.f ? 1.0f : p.scale_log2e;
+      if (p.cap_l2e > 0.f) {
+#pragma unroll
+        for (int c = 0; c < BN; ++c) sc[c] = iert::softcap_l2(sc[c], p.cap_k2, p.cap_l2e);
+      }
       // Scores stay raw; the scale (> 0) is folded into the exponent: p = 2^(s * scale - m).
       // A tile that every row sees entirely (the common case) takes the path without masks.
       const bool need_mask = (j0 + BN - 1 > i0) || (p.window > 0 && j0 < i0 + BM - 1 - (p.window - 1)) || (j0 + BN > len);
@@ -271,7 +278,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         mx = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]);
       }
-      mx *= p.scale_log2e;                                   // -inf stays -inf
+      mx *= sl2;                                   // -inf stays -inf
       const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
       const bool warp_grow = __any_sync(0xffffffffu, grow);
       if (warp_grow) {
@@ -299,7 +306,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // Two scores per instruction (packed fp32 FMA and add).  A masked score is -inf and stays -inf through
       // the FMA (the scale is positive, -m finite), and 2^-inf is 0: masked keys need no select here.
       const float neg_m = m_used == -INFINITY ? 0.f : -m_used;   // a row without a visible key: all p are 0
-      const uint64_t scale2 = pack2(p.scale_log2e, p.scale_log2e), neg_m2 = pack2(neg_m, neg_m);
+      const uint64_t scale2 = pack2(sl2, sl2), neg_m2 = pack2(neg_m, neg_m);
       uint64_t l2a = pack2(0.f, 0.f), l2b = l2a;
       uint32_t pk[BN / 2];
 #pragma unroll
@@ -361,7 +368,7 @@ IERT_API int iert_attention_prefill_tc_available() { return 1; }
 // IERT_BAD_ARGUMENT (nothing launched) when the tensor map cannot be made.
 IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBatchView* batch, int heads,
                                        int kv_heads, int window, float scale, int max_q_len, int* err,
-                                       const float* sink, cudaStream_t stream) {
+                                       const float* sink, float softcap, cudaStream_t stream) {
   if (batch->n_tokens <= 0 || max_q_len <= 0) return IERT_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || (max_q_len + BM - 1) / BM > 65535 || batch->n_seqs > 65535 ||
       ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15))
@@ -376,6 +383,8 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
   p.heads = heads; p.kv_heads = kv_heads; p.window = window;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.sink = sink;
+  p.cap_k2 = softcap > 0.f ? 2.0f * scale * 1.4426950408889634f / softcap : 0.f;
+  p.cap_l2e = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   p.err = err;
   const size_t smem = (size_t)NSUB * SUB_BYTES + 4 * (size_t)NSUB * KV_SUB_BYTES + 256;
   static bool configured = false;
@@ -395,7 +404,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
 
 IERT_API int iert_attention_prefill_tc_available() { return 0; }
 IERT_API int iert_attention_prefill_tc(const void*, void*, const IertBatchView*, int, int, int, float, int, int*, const float*,
-                                       cudaStream_t) {
+                                       float, cudaStream_t) {
   return IERT_BAD_ARGUMENT;
 }
 

@@ -428,17 +428,17 @@ def _attention_lib(head_dim: int):
     if lib is None:
         lib = build.load_library(*build.attention_library(head_dim))
         lib.iert_attention_prefill.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
-                                               c_float, c_int, c_void_p, c_void_p]
+                                               c_float, c_int, c_void_p, c_float, c_void_p]
         lib.iert_attention_prefill.restype = c_int
         lib.iert_attention_decode_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
-                                                 c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]
+                                                 c_float, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p]
         lib.iert_attention_decode_tc.restype = c_int
         lib.iert_attention_decode_tc_rope.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
                                                       c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                                       c_void_p, c_void_p]
         lib.iert_attention_decode_tc_rope.restype = c_int
         lib.iert_attention_prefill_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
-                                                  c_float, c_int, c_void_p, c_void_p, c_void_p]
+                                                  c_float, c_int, c_void_p, c_void_p, c_float, c_void_p]
         lib.iert_attention_prefill_tc.restype = c_int
         lib.iert_attention_prefill_tc_available.restype = c_int
         lib.iert_attention_decode_tc_ctas_per_sm.restype = c_int
@@ -449,12 +449,14 @@ def _attention_lib(head_dim: int):
 
 
 def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, head_dim: int, window: int,
-                      scale: float, max_q_len: int, stream, err=None, legacy: bool = False, sink=None) -> bool:
+                      scale: float, max_q_len: int, stream, err=None, legacy: bool = False, sink=None,
+                      softcap: float = 0.0) -> bool:
     """Flash prompt attention (bf16) over the step's own keys and values.  Head sizes 64 and
     128 run on tcgen05 with the scores and the output in tensor memory (unless `legacy`); other
     multiples of 16 up to 256 run the mma.sync kernel.  The library is compiled per head size
     the first time it is needed; anything else returns False and nothing is launched.  `sink` (fp32
-    [heads], optional): a bare logit per head that adds exp(sink) to each row's softmax denominator only."""
+    [heads], optional): a bare logit per head that adds exp(sink) to each row's softmax denominator only;
+    `softcap` c > 0: scores pass c tanh(s / c) before the softmax."""
     if head_dim % 16 or not 16 <= head_dim <= 256:
         return False
     lib = _attention_lib(head_dim)
@@ -463,14 +465,15 @@ def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, hea
             and os.environ.get("IERT_ATTN_TC", "1") != "0":
         status = lib.iert_attention_prefill_tc(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
                                                window, scale, max_q_len, err.data_ptr(),
-                                               sink.data_ptr() if sink is not None else None, stream)
+                                               sink.data_ptr() if sink is not None else None, softcap, stream)
         if status == 0:
             launch_count += 1
             return True
         if status != 1:
             raise KernelError("attention_prefill_tc: the launch failed")
     status = lib.iert_attention_prefill(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
-                                        window, scale, max_q_len, sink.data_ptr() if sink is not None else None, stream)
+                                        window, scale, max_q_len, sink.data_ptr() if sink is not None else None, softcap,
+                                        stream)
     if status == 1:
         return False
     if status != 0:
@@ -488,14 +491,16 @@ def attention_decode_ctas_per_sm(head_dim: int) -> int:
 
 
 def attention_decode_tc(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: float, splits: int,
-                        scratch, err, stream, target_ctas: int = 0) -> bool:
+                        scratch, err, stream, target_ctas: int = 0, softcap: float = 0.0, sink=None) -> bool:
     """Tensor-core split-KV decode attention (bf16 cache, 64-position pages, head sizes that
-    are multiples of 16 up to 256).  Returns False, having launched nothing, otherwise."""
+    are multiples of 16 up to 256).  Returns False, having launched nothing, otherwise.  `softcap` and
+    `sink` as in `attention_prefill`."""
     hd = kv.head_dim
     if hd % 16 or not 16 <= hd <= 256:
         return False
     status = _attention_lib(hd).iert_attention_decode_tc(qkv.data_ptr(), out.data_ptr(), byref(batch), byref(kv),
                                                          heads, scale, splits, target_ctas, scratch.data_ptr(),
+                                                         softcap, sink.data_ptr() if sink is not None else None,
                                                          err.data_ptr(), stream)
     if status == 1:
         return False

@@ -134,6 +134,15 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
   return __float2bfloat16_rn(x);
 }
 
+// A soft cap on an attention score, in base-2 units: c log2(e) tanh(raw * scale / c), with
+// tanh(x) = 1 - 2 / (2^(2 x log2(e)) + 1).  k2 = 2 scale log2(e) / c, cap_l2e = c log2(e).  The absolute
+// error is about 2^-22 cap_l2e, far below the rounding of the probabilities to bfloat16.
+__device__ __forceinline__ float softcap_l2(float raw, float k2, float cap_l2e) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(raw * k2));
+  return cap_l2e * (1.0f - __fdividef(2.0f, e + 1.0f));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -96,20 +96,21 @@ def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:
     rt = attn.rt
     if qkv.dtype != torch.bfloat16:
         return False
-    softcap, sink = getattr(attn, "softcap", 0.0), getattr(attn, "sink", None)
-    if softcap or sink is not None:
-        return False
+    softcap, sink = float(getattr(attn, "softcap", 0.0) or 0.0), getattr(attn, "sink", None)
     if ctx.kind == "decode":
         splits = decode_splits(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads, attn.head_dim)
         parts, target = decode_parts(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads, ctx.unequal_lengths, attn.head_dim)
         n = B.attention_decode_scratch_floats(ctx.n_tokens, attn.heads, attn.head_dim, max(parts, splits))
         scratch = rt.workspace.take("attn.decode_scratch", (n,), torch.float32)
         if B.attention_decode_tc(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, parts,
-                                 scratch, rt.err, ctx.stream, target_ctas=target):
+                                 scratch, rt.err, ctx.stream, target_ctas=target, softcap=softcap, sink=sink):
             return True
+        if softcap or sink is not None:       # the CUDA-core kernel has neither
+            return False
         return B.attention_decode(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, splits,
                                   scratch, rt.err, ctx.stream)
     if not from_cache:
         return B.attention_prefill(qkv, out, ctx.batch, attn.heads, attn.kv_heads, attn.head_dim,
-                                   attn.window or 0, attn.scale, ctx.max_q_len, ctx.stream, err=rt.err)
+                                   attn.window or 0, attn.scale, ctx.max_q_len, ctx.stream, err=rt.err, sink=sink,
+                                   softcap=softcap)
     return False

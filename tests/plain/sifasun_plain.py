@@ -77,9 +77,13 @@ def rotate_half(v: Tensor, dims: int, base: float, factor: float = 1.0, first_po
 # attention over a sliding window
 
 
-def window_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, window: int, softcap: Optional[float],
+def window_of(m: Mapping) -> Optional[int]:
+    return (m.get("mask") or {}).get("size")
+
+
+def window_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, window: Optional[int], softcap: Optional[float],
                      sink: bool) -> Tensor:
-    """q [T, H, D], k [T, G, D], v [T, G, V] -> [T, H, V].  Token t sees j with 0 <= t - j < window.
+    """q [T, H, D], k [T, G, D], v [T, G, V] -> [T, H, V].  Token t sees j with 0 <= t - j < window (None: all j <= t).
     `softcap` c: score <- c tanh(score / c).  `sink`: one more term exp(0) in the softmax's denominator
     that carries no value."""
     T, H, D = q.shape
@@ -88,7 +92,7 @@ def window_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, window: int,
     for h in range(H):
         g = h // (H // G)
         for t in range(T):
-            lo = max(0, t - window + 1)
+            lo = 0 if window is None else max(0, t - window + 1)
             s = (k[lo:t + 1, g].float() @ q[t, h].float()) * scale
             if softcap is not None:
                 s = softcap * torch.tanh(s / softcap)
@@ -114,7 +118,7 @@ def attention_mixer(x: Tensor, p: Mapping[str, Tensor], m: Mapping, eps: float, 
     factor = float((rot.get("scaling") or {}).get("factor", 1.0))
     q = rms_unit(rotate_half(q, rot["dims"], rot["base"], factor), eps)
     k = rms_unit(rotate_half(k, rot["dims"], rot["base"], factor), eps)
-    o = window_attention(rnd(q), rnd(k), v, float(m["scale"]), m["mask"]["size"], m.get("softcap"), sink=True)
+    o = window_attention(rnd(q), rnd(k), v, float(m["scale"]), window_of(m), m.get("softcap"), sink=True)
     return lin(rnd(o.reshape(T, -1)), p["o"])
 
 
@@ -133,7 +137,7 @@ def left_mixer(x: Tensor, p: Mapping[str, Tensor], m: Mapping, eps: float, rnd: 
     factor = float((rot.get("scaling") or {}).get("factor", 1.0))
     q = rotate_half(q, rot["dims"], rot["base"], factor)
     k = rotate_half(k, rot["dims"], rot["base"], factor)
-    o = window_attention(rnd(q), rnd(k), v, float(m["scale"]), m["mask"]["size"], m.get("softcap"), sink=False)
+    o = window_attention(rnd(q), rnd(k), v, float(m["scale"]), window_of(m), m.get("softcap"), sink=False)
     return lin(rnd(o.reshape(T, -1)), p["left.o"])
 
 
