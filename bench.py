@@ -444,7 +444,7 @@ def main() -> int:
     ap.add_argument("--kernels", action="store_true",
                     help="also time the dominant kernels one by one with CUDA events (projections and decode "
                          "attention at the decode batch, projections at the prefill length): key 'kernels'")
-    ap.add_argument("--design", default=None, choices=["vefulix"],
+    ap.add_argument("--design", default=None, choices=["vefulix", "sifasun"],
                     help="instead of the default workload: prefill and decode of that design at Mistral 7B's width, "
                          "depth (--layers, default 8) and feed-forward size beside Mistral 7B itself, with a table of "
                          "each step's kernels against what their bytes and FLOPs allow (one JSON line)")

@@ -18,7 +18,8 @@ LAUNCHERS = ["embed_gather", "rmsnorm", "rope_kv_store", "silu_mul", "gemm_plain
              "gemm_tc_gated", "gemm_tc_gated_scaled", "attention_prefill", "attention_decode_tc", "attention_decode_tc_rope",
              "attention_decode", "attention_plain", "streams_norm", "streams_expand", "softcap", "delta_prep", "delta_recur",
              "mlstm_recur", "gated_head_norm", "latent_norm_store", "latent_attention_prompt", "latent_attention_decode_tc",
-             "latent_attention_decode", "router_topk", "moe_scale"]
+             "latent_attention_decode", "router_topk", "moe_scale", "add_normed", "cast_rows", "scale_values", "qk_prep",
+             "rglru_conv", "rglru_gates", "rglru_scan"]
 GEMMS = {"gemm_plain", "gemm_tc", "gemm_rows", "gemm_tc_scaled", "gemm_tc_gated", "gemm_tc_gated_scaled"}
 
 
@@ -125,6 +126,24 @@ def _costs(cfg: dict, T: int, n_seqs: int, ctx: int, prompt: bool) -> Dict[str, 
         if mlp:
             inter = mlp["router"]["experts"] * mlp["expert"]["ff"]
             out["moe_scale"] = (0.0, False, T * inter * 4)
+    elif cfg.get("architecture") == "Sifasun":
+        H = cfg["width"]
+        out["add_normed"] = (0.0, False, T * H * 18)
+        out["cast_rows"] = (0.0, False, T * H * 10)
+        by = {l["type"]: l["mixer"] for l in cfg["layers"]}
+        att = by.get("attention") or by["parallel"]["left"]
+        hd, kvd = att["heads"] * att["dim"], att["kv_heads"] * att["dim"]
+        W = (att.get("mask") or {}).get("size") or (1 << 30)
+        seen = T * (T + 1) / 2 if T <= W else W * (W + 1) / 2 + (T - W) * W        # (query, key) pairs inside the window
+        out["attention_prefill"] = (4.0 * hd * seen, True, T * (2 * hd + 2 * kvd) * 2)
+        out["attention_decode_tc"] = (0.0, False, n_seqs * min(ctx, W) * 2 * kvd * 2)
+        out["qk_prep"] = (0.0, False, T * ((hd + kvd) * 4 + (hd + 2 * kvd) * 2 + 2 * kvd * 2))
+        if "parallel" in by:
+            r = by["parallel"]["right"]
+            C, bw = r["width"], r["width"] // r["blocks"]
+            out["rglru_conv"] = (0.0, False, T * C * 8)
+            out["rglru_gates"] = (4.0 * T * C * bw, False, T * C * 12 + 2 * C * bw * 2)
+            out["rglru_scan"] = (0.0, False, T * C * 14 + n_seqs * C * r["conv"] * 8)
     else:
         hd = cfg["num_attention_heads"] * cfg["head_dim"]
         kvd = cfg["num_key_value_heads"] * cfg["head_dim"]

@@ -128,7 +128,7 @@ def _declare(lib) -> None:
                          c_int, P, S],
         "iert_rglru_conv": [P, LL, P, P, P, P, LL, P, c_int, c_int, POINTER(BatchView), S],
         "iert_rglru_gates": [P, P, P, P, P, c_int, P, c_float, P, P, c_int, c_int, c_int, S],
-        "iert_rglru_scan": [P, P, P, LL, P, P, P, LL, P, c_int, c_float, c_int, c_int, POINTER(BatchView), S],
+        "iert_rglru_scan": [P, P, P, LL, P, P, P, LL, P, c_int, c_float, c_int, c_int, c_int, P, POINTER(BatchView), S],
     })
     lib.iert_attention_decode.argtypes = [P, P, POINTER(BatchView), POINTER(KvView), c_int, c_float, c_int, P, P, S]
     lib.iert_attention_decode.restype = c_int
@@ -751,7 +751,15 @@ def rglru_gates(u, ra, ra_b, ri, ri_b, lam, decay_c: float, A, Bv, n_tokens: int
                                   blocks, stream), "rglru_gates")
 
 
-def rglru_scan(A, Bv, proj, by, bx, state, out, out_scale: float, C: int, K: int, batch: BatchView, stream) -> None:
+def rglru_scan_scratch_floats(n_seqs: int, max_q_len: int, C: int) -> int:
+    lib = core()
+    lib.iert_rglru_scan_scratch_floats.restype = c_longlong
+    return int(lib.iert_rglru_scan_scratch_floats(n_seqs, max_q_len, C))
+
+
+def rglru_scan(A, Bv, proj, by, bx, state, out, out_scale: float, C: int, K: int, batch: BatchView, stream,
+               max_q_len: int = 0, scratch=None) -> None:
+    """`max_q_len` and `scratch` (fp32, `rglru_scan_scratch_floats`): long sequences are scanned in chunks (two kernels)."""
     check(core().iert_rglru_scan(A.data_ptr(), Bv.data_ptr(), proj.data_ptr(), proj.stride(0), by.data_ptr(), bx.data_ptr(),
                                  state.data_ptr(), state.stride(0), out.data_ptr(), dtype_code(out.dtype), out_scale, C, K,
-                                 byref(batch), stream), "rglru_scan")
+                                 max_q_len, _ptr(scratch), byref(batch), stream), "rglru_scan")

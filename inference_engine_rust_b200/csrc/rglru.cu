@@ -31,7 +31,9 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// u[t, c] for every token of the step.  proj: fp32 [T, 2C] = [py | px].
+// u[t, c] for every token of the step, a thread per token and channel.  proj: fp32 [T, 2C] = [py | px].
+constexpr int MAX_TAPS = 16;
+
 __global__ void rglru_conv_kernel(const float* __restrict__ proj, long long ld, const float* __restrict__ bx,
                                   const float* __restrict__ taps, const float* __restrict__ cb, const float* __restrict__ state,
                                   long long state_ld, float* __restrict__ u, int C, int K, IertBatchView b) {
@@ -127,8 +129,50 @@ rglru_gates_kernel(const float* __restrict__ u, const TW* __restrict__ Ra, const
   }
 }
 
+// The same for a handful of tokens (one-token steps): a warp per output channel reads its two weight rows once,
+// lanes over k, and forms the sums of up to SMALL_T tokens at a time; the weights are the traffic.
+constexpr int SMALL_T = 8;
+
+template <typename TW>
+__global__ void __launch_bounds__(256)
+rglru_gates_small_kernel(const float* __restrict__ u, const TW* __restrict__ Ra, const float* __restrict__ ra_b,
+                         const TW* __restrict__ Ri, const float* __restrict__ ri_b, const float* __restrict__ lam, float decay_c,
+                         float* __restrict__ A, float* __restrict__ Bv, int T, int C, int bw) {
+  pdl_launch_dependents();
+  const int ch = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (ch >= C) return;
+  const int blk = ch / bw, o = ch - blk * bw;
+  const TW* ra = Ra + ((size_t)blk * bw + o) * bw;
+  const TW* ri = Ri + ((size_t)blk * bw + o) * bw;
+  const float sp = softplus_f(lam[ch]), rb = ra_b[ch], ib = ri_b[ch];
+  pdl_wait();
+  for (int t0 = 0; t0 < T; t0 += SMALL_T) {
+    float ar[SMALL_T], ai[SMALL_T];
+#pragma unroll
+    for (int j = 0; j < SMALL_T; ++j) ar[j] = ai[j] = 0.f;
+    for (int k = lane; k < bw; k += 32) {
+      const float wr = to_f32(ra[k]), wi = to_f32(ri[k]);
+#pragma unroll
+      for (int j = 0; j < SMALL_T; ++j) {
+        const float uv = t0 + j < T ? u[(size_t)(t0 + j) * C + (size_t)blk * bw + k] : 0.f;
+        ar[j] = fmaf(wr, uv, ar[j]);
+        ai[j] = fmaf(wi, uv, ai[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < SMALL_T; ++j) {
+      const float sr = warp_sum(ar[j]), si = warp_sum(ai[j]);
+      if (lane == 0 && t0 + j < T) {
+        const float r = sigmoid_f(sr + rb), g = sigmoid_f(si + ib);
+        const float log_a = -decay_c * r * sp;
+        A[(size_t)(t0 + j) * C + ch] = expf(log_a);
+        Bv[(size_t)(t0 + j) * C + ch] = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f)) * g * u[(size_t)(t0 + j) * C + ch];
+      }
+    }
+  }
+}
+
 // The scan: a thread per (sequence, channel).
-constexpr int MAX_TAPS = 16;
 
 template <typename TO>
 __global__ void rglru_scan_kernel(const float* __restrict__ A, const float* __restrict__ Bv, const float* __restrict__ proj,
@@ -183,6 +227,99 @@ __global__ void rglru_scan_kernel(const float* __restrict__ A, const float* __re
   }
 }
 
+// The scan of long prompts in chunks of SCAN_CHUNK tokens.  A chunk's effect on the state is S -> P S + Q (P the
+// product of its decays, Q its own scan from zero): a first kernel writes (P, Q) of every chunk and the state each
+// sequence starts from; a second one folds the chunks in front of its own, in order, and then walks its chunk as the
+// plain scan does.  The thread of a sequence's last chunk stores S and the new tail of inputs.
+constexpr int SCAN_CHUNK = 64;
+
+__global__ void rglru_chunk_sums_kernel(const float* __restrict__ A, const float* __restrict__ Bv, const float* __restrict__ state,
+                                        long long state_ld, float* __restrict__ PQ, float* __restrict__ S0, int C, int max_chunks,
+                                        IertBatchView b) {
+  pdl_launch_dependents();
+  const int s = blockIdx.z, ch = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int slot = b.slot_ids[s];
+  if (slot < 0 || c >= C) return;
+  const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
+  if (ch * SCAN_CHUNK >= q_len) return;
+  pdl_wait();
+  if (ch == 0) S0[(size_t)s * C + c] = state[(size_t)slot * state_ld + c];
+  const int t0 = q_begin + ch * SCAN_CHUNK, t1 = min(q_begin + q_len, t0 + SCAN_CHUNK);
+  float P = 1.f, Q = 0.f;
+  int t = t0;
+  for (; t + 8 <= t1; t += 8) {
+    float a[8], bv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { a[j] = A[(size_t)(t + j) * C + c]; bv[j] = Bv[(size_t)(t + j) * C + c]; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { P *= a[j]; Q = fmaf(a[j], Q, bv[j]); }
+  }
+  for (; t < t1; ++t) { const float a = A[(size_t)t * C + c]; P *= a; Q = fmaf(a, Q, Bv[(size_t)t * C + c]); }
+  float* pq = PQ + (((size_t)s * max_chunks + ch) * 2) * C;
+  pq[c] = P;
+  pq[C + c] = Q;
+}
+
+template <typename TO>
+__global__ void rglru_chunk_scan_kernel(const float* __restrict__ A, const float* __restrict__ Bv, const float* __restrict__ proj,
+                                        long long ld, const float* __restrict__ by, const float* __restrict__ bx,
+                                        float* __restrict__ state, long long state_ld, const float* __restrict__ PQ,
+                                        const float* __restrict__ S0, TO* __restrict__ out, float out_scale, int C, int K,
+                                        int max_chunks, IertBatchView b) {
+  pdl_launch_dependents();
+  const int s = blockIdx.z, ch = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int slot = b.slot_ids[s];
+  if (slot < 0 || c >= C) return;
+  const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
+  if (ch * SCAN_CHUNK >= q_len) return;
+  const float ybias = by[c], xbias = bx[c];
+  pdl_wait();
+  float S = S0[(size_t)s * C + c];
+  for (int j = 0; j < ch; ++j) {
+    const float* pq = PQ + (((size_t)s * max_chunks + j) * 2) * C;
+    S = fmaf(pq[c], S, pq[C + c]);
+  }
+  const int t0 = q_begin + ch * SCAN_CHUNK, t_end = q_begin + q_len, t1 = min(t_end, t0 + SCAN_CHUNK);
+  int t = t0;
+  for (; t + 4 <= t1; t += 4) {
+    float a[4], bv[4], py[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      a[j] = A[(size_t)(t + j) * C + c];
+      bv[j] = Bv[(size_t)(t + j) * C + c];
+      py[j] = proj[(size_t)(t + j) * ld + c];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      S = fmaf(a[j], S, bv[j]);
+      out[(size_t)(t + j) * C + c] = from_f32<TO>(S * gelu_tanh_f(py[j] + ybias) * out_scale);
+    }
+  }
+  for (; t < t1; ++t) {
+    S = fmaf(A[(size_t)t * C + c], S, Bv[(size_t)t * C + c]);
+    out[(size_t)t * C + c] = from_f32<TO>(S * gelu_tanh_f(proj[(size_t)t * ld + c] + ybias) * out_scale);
+  }
+  if (t1 != t_end) return;
+  float* st = state + (size_t)slot * state_ld;
+  st[c] = S;
+  float* tail = st + C;
+  float keep[MAX_TAPS];
+#pragma unroll
+  for (int i = 0; i < MAX_TAPS; ++i) {
+    if (i >= K - 1) break;
+    const int back = K - 2 - i;
+    if (back < q_len) keep[i] = proj[(size_t)(t_end - 1 - back) * ld + C + c] + xbias;
+    else keep[i] = tail[(size_t)(i + q_len) * C + c];
+  }
+#pragma unroll
+  for (int i = 0; i < MAX_TAPS; ++i) {
+    if (i >= K - 1) break;
+    tail[(size_t)i * C + c] = keep[i];
+  }
+}
+
 }  // namespace
 
 IERT_API int iert_rglru_conv(const float* proj, long long ld, const float* bx, const float* taps, const float* cb,
@@ -204,6 +341,18 @@ IERT_API int iert_rglru_gates(const float* u, const void* Ra, const float* ra_b,
   if (C <= 0 || blocks <= 0 || C % blocks) return IERT_BAD_ARGUMENT;
   const int bw = C / blocks;
   if (blocks > 65535 || (bw + GO - 1) / GO > 65535) return IERT_BAD_ARGUMENT;
+  if (T <= 8 * SMALL_T) {
+    const dim3 g((C + 7) / 8);
+    if (w_dtype == IERT_F32)
+      launch_dep(rglru_gates_small_kernel<float>, g, dim3(256), 0, stream, u, (const float*)Ra, ra_b, (const float*)Ri, ri_b, lam,
+                 decay_c, A, Bv, T, C, bw);
+    else if (w_dtype == IERT_BF16)
+      launch_dep(rglru_gates_small_kernel<__nv_bfloat16>, g, dim3(256), 0, stream, u, (const __nv_bfloat16*)Ra, ra_b,
+                 (const __nv_bfloat16*)Ri, ri_b, lam, decay_c, A, Bv, T, C, bw);
+    else
+      return IERT_BAD_ARGUMENT;
+    return iert_check_launch("rglru_gates");
+  }
   dim3 grid((T + GT - 1) / GT, (bw + GO - 1) / GO, blocks);
   if (w_dtype == IERT_F32)
     launch_dep(rglru_gates_kernel<float>, grid, dim3(GTHREADS), 0, stream, u, (const float*)Ra, ra_b, (const float*)Ri, ri_b,
@@ -216,11 +365,37 @@ IERT_API int iert_rglru_gates(const float* u, const void* Ra, const float* ra_b,
   return iert_check_launch("rglru_gates");
 }
 
+// Floats of scratch the chunked scan needs for sequences of up to `max_q_len` tokens.
+IERT_API long long iert_rglru_scan_scratch_floats(int n_seqs, int max_q_len, int C) {
+  const long long chunks = (max_q_len + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  return (long long)n_seqs * C * (2 * chunks + 1);
+}
+
+// max_q_len: the longest sequence of the step.  With `scratch` (iert_rglru_scan_scratch_floats) sequences of more than
+// two chunks are scanned chunk by chunk; without it, or for short ones, a thread walks its whole sequence.
 IERT_API int iert_rglru_scan(const float* A, const float* Bv, const float* proj, long long ld, const float* by,
                              const float* bx, float* state, long long state_ld, void* out, int out_dtype, float out_scale,
-                             int C, int K, const IertBatchView* batch, cudaStream_t stream) {
+                             int C, int K, int max_q_len, float* scratch, const IertBatchView* batch, cudaStream_t stream) {
   if (batch->n_tokens <= 0 || batch->n_seqs <= 0) return IERT_OK;
   if (C <= 0 || K < 1 || K > MAX_TAPS || batch->n_seqs > 65535) return IERT_BAD_ARGUMENT;
+  if (scratch && max_q_len > 2 * SCAN_CHUNK) {
+    const int chunks = (max_q_len + SCAN_CHUNK - 1) / SCAN_CHUNK;
+    if (chunks > 65535) return IERT_BAD_ARGUMENT;
+    float* S0 = scratch;
+    float* PQ = scratch + (size_t)batch->n_seqs * C;
+    const int th = 128;
+    dim3 grid((C + th - 1) / th, chunks, batch->n_seqs);
+    launch_dep(rglru_chunk_sums_kernel, grid, dim3(th), 0, stream, A, Bv, (const float*)state, state_ld, PQ, S0, C, chunks, *batch);
+    if (out_dtype == IERT_F32)
+      launch_dep(rglru_chunk_scan_kernel<float>, grid, dim3(th), 0, stream, A, Bv, proj, ld, by, bx, state, state_ld,
+                 (const float*)PQ, (const float*)S0, (float*)out, out_scale, C, K, chunks, *batch);
+    else if (out_dtype == IERT_BF16)
+      launch_dep(rglru_chunk_scan_kernel<__nv_bfloat16>, grid, dim3(th), 0, stream, A, Bv, proj, ld, by, bx, state, state_ld,
+                 (const float*)PQ, (const float*)S0, (__nv_bfloat16*)out, out_scale, C, K, chunks, *batch);
+    else
+      return IERT_BAD_ARGUMENT;
+    return iert_check_launch("rglru_scan");
+  }
   const int threads = C >= 4096 ? 128 : 64;
   dim3 grid((C + threads - 1) / threads, batch->n_seqs);
   if (out_dtype == IERT_F32)

@@ -87,7 +87,11 @@ class RecurrentGatedUnit(Mixer):
         B.rglru_gates(u, self.ra, self.ra_b, self.ri, self.ri_b, self.lam, self.decay_constant, a, bv, T, C, self.blocks,
                       ctx.stream)
         out = ws.take("rglru.out", (T, C), rt.dtype)
-        B.rglru_scan(a, bv, proj, self.by, self.bx, state, out, self.out_scale, C, self.taps, ctx.batch, ctx.stream)
+        scratch = None
+        if ctx.kind == "prompt" and ctx.max_q_len > 128:       # long prompts: the scan in chunks
+            scratch = ws.take("rglru.chunks", (B.rglru_scan_scratch_floats(ctx.n_seqs, ctx.max_q_len, C),), torch.float32)
+        B.rglru_scan(a, bv, proj, self.by, self.bx, state, out, self.out_scale, C, self.taps, ctx.batch, ctx.stream,
+                     max_q_len=ctx.max_q_len, scratch=scratch)
         self.o.apply(out, residual, T, ctx.stream, add_residual=True)
 
 
