@@ -448,11 +448,16 @@ def main() -> int:
                     help="instead of the default workload: prefill and decode of that design at Mistral 7B's width, "
                          "depth (--layers, default 8) and feed-forward size beside Mistral 7B itself, with a table of "
                          "each step's kernels against what their bytes and FLOPs allow (one JSON line)")
+    ap.add_argument("--design-sizes", default="7b", choices=["7b", "12b"],
+                    help="with --design sifasun: the sizes of Mistral 7B (default) or of Mistral NeMo 12B")
     a = ap.parse_args()
 
     if a.design is not None and a.impl != "reference":
         from inference_engine_rust_b200 import bench_designs
-        print(json.dumps(bench_designs.compare(f"{a.design}-7b-sizes", "7b-v0.1", a.layers or 8, peaks(), a.batch, a.context,
+        if a.design_sizes == "12b" and a.design != "sifasun":
+            ap.error("--design-sizes 12b is there for --design sifasun only")
+        base = "7b-v0.1" if a.design_sizes == "7b" else "nemo-12b"
+        print(json.dumps(bench_designs.compare(f"{a.design}-{a.design_sizes}-sizes", base, a.layers or 8, peaks(), a.batch, a.context,
                                                a.prefill_tokens, min(a.steps, 32), max(3, min(a.warmup, 4)))))
         return 0
     if a.impl == "reference":

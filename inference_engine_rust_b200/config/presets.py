@@ -77,6 +77,8 @@ def _sifasun(width, vocab, layers, heads, kv_heads, dim, ff, lru_width, blocks, 
 # Sifasun at the width, head count, head size and feed-forward size of Mistral 7B (a recurrence as wide as the model in
 # 16 blocks), and a tiny one that runs anywhere in seconds (its last four layers run with the first four's weights).
 PRESETS["sifasun-7b-sizes"] = _sifasun(4096, 32000, 32, 32, 8, 128, 14336, 4096, 16, 2048)
+# the same at the sizes of Mistral NeMo 12B (width 5,120, a vocabulary of 131,072)
+PRESETS["sifasun-12b-sizes"] = _sifasun(5120, 131072, 40, 32, 8, 128, 14336, 5120, 16, 2048)
 PRESETS["sifasun-tiny"] = _sifasun(96, 320, 8, 4, 2, 16, 160, 64, 4, 24, shared_from=4)
 
 

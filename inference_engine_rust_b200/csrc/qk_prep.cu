@@ -47,6 +47,8 @@ qk_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ qkv
   const bool store = write_cache && pos >= final_len - c.ring_pages * c.page_tokens;
   const float* pr = proj + (size_t)t * ld;
   T* out = qkv + (size_t)t * (qd + 2 * kd);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_heads = heads + nkv;
+  constexpr int WARPS = THREADS / 32;
   float ssq = 0.f, ssk = 0.f;
   for (int i = threadIdx.x; i < qd + kd; i += THREADS) {
     const float v = pr[i];
@@ -59,52 +61,47 @@ qk_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ qkv
   } else {
     __syncthreads();
   }
-  // the values: the keys as projected
-  for (int i = threadIdx.x; i < kd; i += THREADS) {
-    const T v = from_f32<T>(row[qd + i] * value_scale);
-    out[qd + kd + i] = v;
-    if (store) {
-      const int h = i / hd, d = i - h * hd;
-      const long long off = kv_row_offset(c, slot, pos, h, err);
+  // the values: the keys as projected (a warp per head: the place in the cache is worked out once per head)
+  for (int h = warp; h < nkv; h += WARPS) {
+    const long long off = store ? kv_row_offset(c, slot, pos, h, err) : -1;
+    const float* src = row + qd + (size_t)h * hd;
+    T* dst = out + qd + kd + (size_t)h * hd;
+    for (int d = lane; d < hd; d += 32) {
+      const T v = from_f32<T>(src[d] * value_scale);
+      dst[d] = v;
       if (off >= 0) ((T*)c.v)[off + d] = v;
     }
   }
-  if (norm_mode == 1) {
-    const float rq = 1.0f / sqrtf(ssq / (float)qd + eps), rk = 1.0f / sqrtf(ssk / (float)kd + eps);
-    __syncthreads();
-    for (int i = threadIdx.x; i < qd + kd; i += THREADS)
-      row[i] = i < qd ? row[i] * rq * wq[i] : row[i] * rk * wk[i - qd];
-  }
+  const float rq = 1.0f / sqrtf(ssq / (float)qd + eps), rk = 1.0f / sqrtf(ssk / (float)kd + eps);
   __syncthreads();
-  // rotation: one thread per pair
-  const int n_heads = heads + nkv;
-  for (int i = threadIdx.x; i < n_heads * half; i += THREADS) {
-    const int h = i / half, k = i - h * half;
+  // per head: the whole-projection norm's factor and weight, the rotation, the unit norm, the rounding and the stores
+  for (int h = warp; h < n_heads; h += WARPS) {
     float* v = row + (size_t)h * hd;
-    const float a = v[k], bb = v[k + half];
-    v[k] = a * cs[k] - bb * cs[half + k];
-    v[k + half] = bb * cs[k] + a * cs[half + k];
-  }
-  __syncthreads();
-  if (norm_mode == 2) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int h = warp; h < n_heads; h += THREADS / 32) {
-      float* v = row + (size_t)h * hd;
+    if (norm_mode == 1) {
+      const float r = h < heads ? rq : rk;
+      const float* w = h < heads ? wq + (size_t)h * hd : wk + (size_t)(h - heads) * hd;
+      for (int d = lane; d < hd; d += 32) v[d] *= r * w[d];
+      __syncwarp();
+    }
+    for (int k = lane; k < half; k += 32) {
+      const float a = v[k], bb = v[k + half];
+      v[k] = a * cs[k] - bb * cs[half + k];
+      v[k + half] = bb * cs[k] + a * cs[half + k];
+    }
+    __syncwarp();
+    float r = 1.f;
+    if (norm_mode == 2) {
       float ss = 0.f;
       for (int d = lane; d < hd; d += 32) ss = fmaf(v[d], v[d], ss);
       ss = warp_sum(ss);
-      const float r = 1.0f / sqrtf(ss / (float)hd + eps);
-      for (int d = lane; d < hd; d += 32) v[d] *= r;
+      r = 1.0f / sqrtf(ss / (float)hd + eps);
     }
-    __syncthreads();
-  }
-  for (int i = threadIdx.x; i < qd + kd; i += THREADS) {
-    const T v = from_f32<T>(row[i]);
-    out[i] = v;
-    if (store && i >= qd) {
-      const int j = i - qd, h = j / hd, d = j - h * hd;
-      const long long off = kv_row_offset(c, slot, pos, h, nullptr);
-      if (off >= 0) ((T*)c.k)[off + d] = v;
+    T* dst = out + (size_t)h * hd;
+    const long long off = (store && h >= heads) ? kv_row_offset(c, slot, pos, h - heads, nullptr) : -1;
+    for (int d = lane; d < hd; d += 32) {
+      const T o = from_f32<T>(v[d] * r);
+      dst[d] = o;
+      if (off >= 0) ((T*)c.k)[off + d] = o;
     }
   }
 }

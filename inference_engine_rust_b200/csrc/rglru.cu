@@ -58,6 +58,57 @@ __global__ void rglru_conv_kernel(const float* __restrict__ proj, long long ld, 
   u[(size_t)t * C + c] = acc;
 }
 
+// The same with four consecutive channels per thread (16-byte accesses) and CONV_TOKENS tokens per block, which
+// brings its channels' taps into shared memory once, transposed (taps of one place side by side).  C a multiple of 4,
+// rows aligned.
+constexpr int CONV_TOKENS = 4, CONV_THREADS = 128;
+
+__global__ void __launch_bounds__(CONV_THREADS)
+rglru_conv4_kernel(const float* __restrict__ proj, long long ld, const float* __restrict__ bx,
+                   const float* __restrict__ taps, const float* __restrict__ cb, const float* __restrict__ state,
+                   long long state_ld, float* __restrict__ u, int C, int K, IertBatchView b) {
+  extern __shared__ __align__(16) float taps_s[];             // [K][4 * CONV_THREADS]
+  pdl_launch_dependents();
+  constexpr int CH = 4 * CONV_THREADS;
+  const int c0 = blockIdx.y * CH;
+  const int c = c0 + threadIdx.x * 4;
+  const int n_ch = min(CH, C - c0);
+  for (int i = threadIdx.x; i < n_ch * K; i += CONV_THREADS) {
+    const int ch = i / K, q = i - ch * K;
+    taps_s[q * CH + ch] = taps[(size_t)c0 * K + i];
+  }
+  __syncthreads();
+  if (c >= C) return;
+  const float4 bias = *reinterpret_cast<const float4*>(bx + c);
+  const float4 cbias = *reinterpret_cast<const float4*>(cb + c);
+  pdl_wait();
+  for (int i = 0; i < CONV_TOKENS; ++i) {
+    const int t = blockIdx.x * CONV_TOKENS + i;
+    if (t >= b.n_tokens) break;
+    const int s = sequence_of_token(b, t);
+    const int slot = s < 0 ? -1 : b.slot_ids[s];
+    if (slot < 0) continue;
+    const int back = t - b.cu_q[s];
+    const float* tail = state + (size_t)slot * state_ld + C;
+    float4 acc = cbias;
+    for (int j = K - 1; j >= 0; --j) {
+      float4 xin;
+      if (j <= back) {
+        xin = *reinterpret_cast<const float4*>(proj + (size_t)(t - j) * ld + C + c);
+        xin.x += bias.x; xin.y += bias.y; xin.z += bias.z; xin.w += bias.w;
+      } else {
+        xin = *reinterpret_cast<const float4*>(tail + (size_t)(K - 1 - (j - back)) * C + c);
+      }
+      const float4 w = *reinterpret_cast<const float4*>(taps_s + (K - 1 - j) * CH + threadIdx.x * 4);
+      acc.x = fmaf(w.x, xin.x, acc.x);
+      acc.y = fmaf(w.y, xin.y, acc.y);
+      acc.z = fmaf(w.z, xin.z, acc.z);
+      acc.w = fmaf(w.w, xin.w, acc.w);
+    }
+    *reinterpret_cast<float4*>(u + (size_t)t * C + c) = acc;
+  }
+}
+
 // Gates, decay and input term: A[t, c] = a, Bv[t, c] = sqrt(1 - a^2) i u.
 // Tile: 32 tokens x 64 output channels of one block, k in chunks of 32.
 constexpr int GT = 32, GO = 64, GK = 32, GTHREADS = 256;
@@ -125,6 +176,134 @@ rglru_gates_kernel(const float* __restrict__ u, const TW* __restrict__ Ra, const
       const float m = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f));       // sqrt(1 - a^2) without cancellation
       A[(size_t)t * C + ch] = av;
       Bv[(size_t)t * C + ch] = m * g * u[(size_t)t * C + ch];
+    }
+  }
+}
+
+// The gates of many tokens with bfloat16 weights, on the tensor cores (mma.sync m16n8k16) without giving up the
+// 32-bit input: u is split as hi + lo, two bfloat16 numbers that together carry 16 bits of its mantissa, both are
+// multiplied by the (exact) bfloat16 weights and summed in fp32, so a sum differs from the fp32 one by about 2^-17 of
+// its terms.  Tile: 64 tokens x 64 output channels of one block, both gates; a warp owns 16 tokens; k in chunks of 32.
+constexpr int TM = 64, TN = 64, TK = 32, TLD = TK + 8, TC_THREADS = 128;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(TC_THREADS)
+rglru_gates_tc_kernel(const float* __restrict__ u, const __nv_bfloat16* __restrict__ Ra, const float* __restrict__ ra_b,
+                      const __nv_bfloat16* __restrict__ Ri, const float* __restrict__ ri_b, const float* __restrict__ lam,
+                      float decay_c, float* __restrict__ A, float* __restrict__ Bv, int T, int C, int bw) {
+  __shared__ __align__(16) __nv_bfloat16 a_hi[TM][TLD];
+  __shared__ __align__(16) __nv_bfloat16 a_lo[TM][TLD];
+  __shared__ __align__(16) __nv_bfloat16 w_r[TN][TLD];
+  __shared__ __align__(16) __nv_bfloat16 w_i[TN][TLD];
+  pdl_launch_dependents();
+  const int blk = blockIdx.z, o0 = blockIdx.y * TN, t0 = blockIdx.x * TM;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const __nv_bfloat16* ra = Ra + (size_t)blk * bw * bw;
+  const __nv_bfloat16* ri = Ri + (size_t)blk * bw * bw;
+  float cr[TN / 8][4], ci[TN / 8][4];
+#pragma unroll
+  for (int n = 0; n < TN / 8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) cr[n][e] = ci[n][e] = 0.f;
+  pdl_wait();
+  // A chunk's operands come from memory into registers while the chunk before it is multiplied.
+  constexpr int UV = TM * TK / 4 / TC_THREADS, WV = TN * TK / 8 / TC_THREADS;
+  float4 ureg[UV];
+  uint4 wreg_r[WV], wreg_i[WV];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int q = 0; q < UV; ++q) {                 // u: 64 tokens x 32 k, four consecutive k per load
+      const int i = threadIdx.x + q * TC_THREADS;
+      const int tt = i / (TK / 4), kk = (i - tt * (TK / 4)) * 4;
+      const int t = t0 + tt, k = k0 + kk;
+      ureg[q] = (t < T && k < bw) ? *reinterpret_cast<const float4*>(u + (size_t)t * C + (size_t)blk * bw + k)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int q = 0; q < WV; ++q) {                 // weights: 64 output rows x 32 k of either gate, eight k per load
+      const int i = threadIdx.x + q * TC_THREADS;
+      const int oo = i / (TK / 8), kk = (i - oo * (TK / 8)) * 8;
+      const int o = o0 + oo, k = k0 + kk;
+      const bool in = o < bw && k < bw;
+      wreg_r[q] = in ? *reinterpret_cast<const uint4*>(ra + (size_t)o * bw + k) : make_uint4(0u, 0u, 0u, 0u);
+      wreg_i[q] = in ? *reinterpret_cast<const uint4*>(ri + (size_t)o * bw + k) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < bw; k0 += TK) {
+#pragma unroll
+    for (int q = 0; q < UV; ++q) {                 // u as hi and lo
+      const int i = threadIdx.x + q * TC_THREADS;
+      const int tt = i / (TK / 4), kk = (i - tt * (TK / 4)) * 4;
+      const float4 v = ureg[q];
+      const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+      const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);
+      const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2bfloat162_rn(v.z - f1.x, v.w - f1.y);
+      *reinterpret_cast<__nv_bfloat162*>(&a_hi[tt][kk]) = h0;
+      *reinterpret_cast<__nv_bfloat162*>(&a_hi[tt][kk + 2]) = h1;
+      *reinterpret_cast<__nv_bfloat162*>(&a_lo[tt][kk]) = l0;
+      *reinterpret_cast<__nv_bfloat162*>(&a_lo[tt][kk + 2]) = l1;
+    }
+#pragma unroll
+    for (int q = 0; q < WV; ++q) {
+      const int i = threadIdx.x + q * TC_THREADS;
+      const int oo = i / (TK / 8), kk = (i - oo * (TK / 8)) * 8;
+      *reinterpret_cast<uint4*>(&w_r[oo][kk]) = wreg_r[q];
+      *reinterpret_cast<uint4*>(&w_i[oo][kk]) = wreg_i[q];
+    }
+    __syncthreads();
+    if (k0 + TK < bw) fetch(k0 + TK);
+#pragma unroll
+    for (int ks = 0; ks < TK / 16; ++ks) {
+      uint32_t ah[4], al[4];
+      ldsm_x4(ah, &a_hi[warp * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+      ldsm_x4(al, &a_lo[warp * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int np = 0; np < TN / 16; ++np) {
+        uint32_t br[4], bi[4];
+        const int row = np * 16 + (lane & 7) + ((lane >> 4) << 3), col = ks * 16 + ((lane >> 3) & 1) * 8;
+        ldsm_x4(br, &w_r[row][col]);
+        ldsm_x4(bi, &w_i[row][col]);
+        mma_bf16_16816(cr[2 * np], al, br[0], br[1]);          // the small parts first
+        mma_bf16_16816(cr[2 * np + 1], al, br[2], br[3]);
+        mma_bf16_16816(ci[2 * np], al, bi[0], bi[1]);
+        mma_bf16_16816(ci[2 * np + 1], al, bi[2], bi[3]);
+        mma_bf16_16816(cr[2 * np], ah, br[0], br[1]);
+        mma_bf16_16816(cr[2 * np + 1], ah, br[2], br[3]);
+        mma_bf16_16816(ci[2 * np], ah, bi[0], bi[1]);
+        mma_bf16_16816(ci[2 * np + 1], ah, bi[2], bi[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int n = 0; n < TN / 8; ++n) {
+    const int o = o0 + n * 8 + tq * 2;
+    if (o >= bw) continue;                             // bw is even: o + 1 is inside too
+    const size_t ch = (size_t)blk * bw + o;
+    const float sp0 = softplus_f(lam[ch]), sp1 = softplus_f(lam[ch + 1]);
+    const float rb0 = ra_b[ch], rb1 = ra_b[ch + 1], ib0 = ri_b[ch], ib1 = ri_b[ch + 1];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int t = t0 + warp * 16 + g + 8 * half;
+      if (t >= T) continue;
+      const float2 uv = *reinterpret_cast<const float2*>(u + (size_t)t * C + ch);
+      const float la0 = -decay_c * sigmoid_f(cr[n][2 * half] + rb0) * sp0;
+      const float la1 = -decay_c * sigmoid_f(cr[n][2 * half + 1] + rb1) * sp1;
+      *reinterpret_cast<float2*>(A + (size_t)t * C + ch) = make_float2(expf(la0), expf(la1));
+      *reinterpret_cast<float2*>(Bv + (size_t)t * C + ch) =
+          make_float2(sqrtf(fmaxf(-expm1f(2.0f * la0), 0.f)) * sigmoid_f(ci[n][2 * half] + ib0) * uv.x,
+                      sqrtf(fmaxf(-expm1f(2.0f * la1), 0.f)) * sigmoid_f(ci[n][2 * half + 1] + ib1) * uv.y);
     }
   }
 }
@@ -327,6 +506,13 @@ IERT_API int iert_rglru_conv(const float* proj, long long ld, const float* bx, c
                              cudaStream_t stream) {
   if (batch->n_tokens <= 0) return IERT_OK;
   if (C <= 0 || K < 1 || K > MAX_TAPS) return IERT_BAD_ARGUMENT;
+  if (C % 4 == 0 && ld % 4 == 0 && state_ld % 4 == 0 &&
+      (((uintptr_t)proj | (uintptr_t)bx | (uintptr_t)cb | (uintptr_t)state | (uintptr_t)u) & 15) == 0) {
+    const int ch = 4 * CONV_THREADS;
+    launch_dep(rglru_conv4_kernel, dim3((batch->n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (C + ch - 1) / ch), dim3(CONV_THREADS),
+               (size_t)K * ch * sizeof(float), stream, proj, ld, bx, taps, cb, state, state_ld, u, C, K, *batch);
+    return iert_check_launch("rglru_conv");
+  }
   const int threads = C >= 256 ? 256 : 64;
   launch_dep(rglru_conv_kernel, dim3(batch->n_tokens, (C + threads - 1) / threads), dim3(threads), 0, stream, proj, ld, bx,
              taps, cb, state, state_ld, u, C, K, *batch);
@@ -351,6 +537,13 @@ IERT_API int iert_rglru_gates(const float* u, const void* Ra, const float* ra_b,
                  (const __nv_bfloat16*)Ri, ri_b, lam, decay_c, A, Bv, T, C, bw);
     else
       return IERT_BAD_ARGUMENT;
+    return iert_check_launch("rglru_gates");
+  }
+  // bfloat16 weights, blocks in whole runs of eight and everything aligned for the vector loads: the tensor cores
+  if (w_dtype == IERT_BF16 && bw % 8 == 0 && (((uintptr_t)u | (uintptr_t)A | (uintptr_t)Bv | (uintptr_t)Ra | (uintptr_t)Ri) & 15) == 0 &&
+      (bw + TN - 1) / TN <= 65535) {
+    launch_dep(rglru_gates_tc_kernel, dim3((T + TM - 1) / TM, (bw + TN - 1) / TN, blocks), dim3(TC_THREADS), 0, stream, u,
+               (const __nv_bfloat16*)Ra, ra_b, (const __nv_bfloat16*)Ri, ri_b, lam, decay_c, A, Bv, T, C, bw);
     return iert_check_launch("rglru_gates");
   }
   dim3 grid((T + GT - 1) / GT, (bw + GO - 1) / GO, blocks);

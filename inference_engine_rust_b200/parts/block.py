@@ -155,7 +155,8 @@ class OutputNormBlock(Block):
         y = rt.workspace.take("block.sublayer_out", x.shape, torch.float32)
         h = rt.workspace.take("block.input", x.shape, rt.dtype)
         ahead, ctx.rows_ahead = ctx.rows_ahead, None
-        if not (isinstance(ahead, CastAhead) and ahead.rows is x and ahead.cast is h and ahead.cleared is y):
+        if not (isinstance(ahead, CastAhead) and ahead.rows is x and ahead.cast.data_ptr() == h.data_ptr()
+                and ahead.cleared.data_ptr() == y.data_ptr() and ahead.cast.dtype == h.dtype):
             B.cast_rows(x, y, h, T, ctx.stream)
         self.mixer.forward(h, y, ctx, cache_view, writes_cache)
         self.norm1.add_normed(y, x, h, ctx, T)

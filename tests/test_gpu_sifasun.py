@@ -104,7 +104,14 @@ TENSOR = config([layer("attention", attn(heads=4, kv_heads=2, dim=64, window=100
                                         right={"width": 128, "blocks": 2, "conv": 4}), ff=128),
                  layer("attention", attn(heads=4, kv_heads=4, dim=32, window=40, scale=0.4, softcap=5.0, rot_dims=16), ff=None)],
                 width=128, vocab=256)
-WHOLE_MODELS = {"full": FULL, "odd": ODD, "tensor": TENSOR}
+# heads of 128 (tcgen05 prompt attention, decode attention with pages by TMA) and recurrence blocks of 128 channels
+# (several tiles of the tensor-core gates)
+WIDE_HEADS = config([layer("attention", attn(heads=4, kv_heads=2, dim=128, window=150, scale=0.2, softcap=10.0, rot_dims=64), ff=None),
+                     layer("parallel", pair(left=attn(heads=2, kv_heads=1, dim=128, window=90, scale=0.15, softcap=None,
+                                                      rot_dims=128, factor=None),
+                                            right={"width": 256, "blocks": 2, "conv": 4}), ff=256)],
+                    width=256, vocab=160)
+WHOLE_MODELS = {"full": FULL, "odd": ODD, "tensor": TENSOR, "wide_heads": WIDE_HEADS}
 
 
 def sharpen(tensors):
