@@ -60,10 +60,10 @@ def _sifasun(width, vocab, layers, heads, kv_heads, dim, ff, lru_width, blocks, 
     layers, round and round; from layer `shared_from` on, layers run with the weights of the layer that many places
     before them."""
     attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
-                 "mask": {"size": window}, "rot": {"base": 500000.0, "dims": dim // 2, "scaling": {"factor": 4.0}}}
+                 "mask": {"size": window}, "rot": {"base": 1000000.0, "dims": dim // 2, "scaling": {"factor": 8.0}}}
     left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-            "mask": {"size": 2 * window}, "rot": {"base": 250000.0, "dims": dim}}
-    pair = {"left": left, "left_scale": 1.1, "right": {"width": lru_width, "blocks": blocks, "conv": 4}, "right_scale": 0.9}
+            "mask": {"size": 2 * window}, "rot": {"base": 10000.0, "dims": dim}}
+    pair = {"left": left, "left_scale": 1.1, "right": {"width": lru_width, "blocks": blocks, "conv": 4}, "right_scale": 0.8}
     out = []
     for i in range(layers):
         entry = {"type": "parallel" if i % 4 == 0 else "attention", "mixer": dict(pair if i % 4 == 0 else attention),

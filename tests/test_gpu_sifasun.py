@@ -389,3 +389,30 @@ def test_trace_replay_program(root, tmp_path, dtype):
     R.replay(d, dtype, steps, out, max_tokens=64 * 9)
     for step, rows in wanted:
         compare(R.read(out, step, cfg["vocab"]), torch.stack(rows), dtype, f"step {step}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompt_steps_replayed_as_graphs(root, dtype):
+    """Prompt steps of up to 512 tokens that want their last rows are captured into a CUDA graph from a shape
+    bucket's second use on (padding tokens and padding sequences inside; the recurrence's scan in chunks for the
+    longer buckets): same logits as the plain statement on every turn, with state, slots and pages used again in
+    between, and the tokens after the prompt one by one."""
+    cfg = WHOLE_MODELS["tensor" if dtype == "bfloat16" else "full"]
+    model, weights = make_model(root, cfg, 17, dtype)
+    prompts = tokens(cfg, (3, 1, 63, 200, 140, 331), seed=8)
+    want = [P.forward(cfg, weights, p + [5, 6], rounding(dtype)) for p in prompts]
+    eng = engine_of(model, max_tokens=64 * 14, max_sequences=4)
+    batches = [[1, 0], [3], [1, 2], [4, 0], [5], [0, 1], [3, 1], [2, 1], [5], [4]]
+    for turn, batch in enumerate(batches * 2):
+        slots = [eng.open_sequence() for _ in batch]
+        got = eng.step([(s, prompts[i]) for s, i in zip(slots, batch)], want="last")
+        more = eng.step([(s, [5]) for s in slots], want="last")
+        last = eng.step([(s, [6]) for s in slots], want="last")
+        eng.check_device()
+        for k, i in enumerate(batch):
+            n = len(prompts[i])
+            compare(torch.cat([got[k:k + 1], more[k:k + 1], last[k:k + 1]]), want[i][n - 1:], dtype,
+                    f"turn {turn}: a {n}-token prompt and two tokens more")
+        for s in slots:
+            eng.close_sequence(s)
+    assert sum(1 for k in eng._graphs if isinstance(k, tuple) and k and k[0] == "prompt") >= 4, "few prompt steps were replayed"
