@@ -33,7 +33,14 @@ qk_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ qkv
   const int t = blockIdx.x;
   const int s = sequence_of_token(b, t);
   const int slot = s < 0 ? -1 : b.slot_ids[s];
-  if (slot < 0) return;
+  if (slot < 0) {
+    // a padding token: a defined row (the prompt attention kernels read whole tiles of keys and values, and a masked
+    // key's weight of zero times a NaN left in this row would still be NaN)
+    pdl_wait();
+    T* pad = qkv + (size_t)t * (qd + 2 * kd);
+    for (int i = threadIdx.x; i < qd + 2 * kd; i += THREADS) pad[i] = from_f32<T>(0.f);
+    return;
+  }
   const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
   const int pos = b.pos0[s] + (t - q_begin);
   const int final_len = b.pos0[s] + q_len;
