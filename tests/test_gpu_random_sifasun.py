@@ -17,7 +17,7 @@ COUNT = int(os.environ.get("IERT_TEST_RANDOM_SIFASUN", "8"))
 
 
 def draw_attention(rng, left):
-    dim = rng.choice([8, 16, 24, 32, 48, 64, 80, 128])
+    dim = rng.choice([8, 16, 24, 32, 48, 64, 80, 96, 128, 160, 256])
     kv = rng.choice([1, 2, 3, 4])
     rot = rng.choice([0, dim // 4 * 2, dim // 2, dim]) // 2 * 2
     return T.attn(heads=kv * rng.choice([1, 2, 3, 5]), kv_heads=kv, dim=dim, window=rng.choice([None, 1, 2, 7, 33, 64, 65, 100, 200]),
@@ -83,4 +83,5 @@ def test_random_configuration(root, case):
                 live.remove(i)
         eng.check_device()
         for i in range(len(prompts)):
-            T.compare(torch.cat(rows[i]), want[i], dtype, f"case {case} ({dtype}), request {i}: {cfg}")
+            T.compare(torch.cat(rows[i]), want[i], dtype, f"case {case} ({dtype}), request {i}: {cfg}",
+                      slack=max(1.0, len(layers) / 5))

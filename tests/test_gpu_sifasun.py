@@ -19,24 +19,26 @@ from plain import sifasun_plain as P
 pytestmark = pytest.mark.gpu
 
 
-def compare(got, ref, dtype, what=""):
+def compare(got, ref, dtype, what="", slack=1.0):
     """float32: the library's bound for 32-bit runs (every logit within 2e-4, absolute + relative).
     bfloat16: both sides round activations to bfloat16, but not at exactly the same places (the engine keeps the
     projections that enter norms and the recurrence in 32-bit and rounds its attention weights), and these
     models' softmaxes are sharp on purpose, which carries a rounding of a score on.  So rows are judged one by
     one: the root-mean-square error of a row against the largest logit must be below 1.2 % for all but 15 % of
     the rows (at least two), below 0.6 % for the median row, and below 30 % for every row.  A fault of the
-    cache, the state or the batch hits most rows, and every case also runs in float32."""
+    cache, the state or the batch hits most rows, and every case also runs in float32.  `slack` widens the bfloat16
+    bounds for models of many layer runs, whose roundings add up (measured on such a model: the engine and the plain
+    statement with its bfloat16 roundings are equally far from the 32-bit result)."""
     if dtype == "float32":
         return compare_exactly(got, ref, dtype, what)
     got, ref = torch.as_tensor(got).float().cpu(), torch.as_tensor(ref).float().cpu()
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite values"
     rows = (got - ref).pow(2).mean(-1).sqrt() / ref.abs().max()
-    over = int((rows > 0.012).sum())
+    over = int((rows > 0.012 * slack).sum())
     assert rows.max() < 0.3, f"{what}: row {int(rows.argmax())} is off by {rows.max().item():.3g} of the largest logit"
     assert over <= max(2, int(0.15 * len(rows))), f"{what}: {over} of {len(rows)} rows are off (worst {rows.max().item():.3g})"
-    assert len(rows) < 8 or rows.median() < 0.006, f"{what}: the median row is off by {rows.median().item():.3g}"
+    assert len(rows) < 8 or rows.median() < 0.006 * slack, f"{what}: the median row is off by {rows.median().item():.3g}"
 
 
 def attn(heads=4, kv_heads=2, dim=16, window=9, scale=0.6, softcap=7.0, rot_dims=8, base=900.0, factor=3.0):
