@@ -127,9 +127,17 @@ IERT_API int iert_qk_prep(const float* proj, long long ld, void* qkv, int dtype,
     return IERT_BAD_ARGUMENT;
   const size_t smem = ((size_t)(heads + cache->kv_heads) * hd + rotary_dim) * sizeof(float);
   if (smem > 200 * 1024) return IERT_BAD_ARGUMENT;
+  // the opt-in for more than 48 KB of dynamic shared memory, asked once per size (and not again inside a stream capture)
 #define GO(T)                                                                                                          \
   do {                                                                                                                 \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(qk_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    static size_t allowed = 48 * 1024;                                                                                 \
+    if (smem > allowed) {                                                                                              \
+      if (cudaFuncSetAttribute(qk_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { \
+        cudaGetLastError();                                                                                            \
+        return IERT_BAD_ARGUMENT;                                                                                      \
+      }                                                                                                                \
+      allowed = smem;                                                                                                  \
+    }                                                                                                                  \
     launch_dep(qk_prep_kernel<T>, dim3(batch->n_tokens), dim3(THREADS), smem, stream, proj, ld, (T*)qkv, *batch, *cache,    \
                heads, inv_freq, rotary_dim, norm_mode, wq, wk, eps, value_scale, write_cache, err);                      \
   } while (0)

@@ -77,6 +77,8 @@ ALONE = {
     "attention_whole_head_turns_one_kv_head": [layer("attention", attn(heads=3, kv_heads=1, dim=32, rot_dims=32, window=70), ff=None)],
     "attention_nothing_turns": [layer("attention", attn(heads=2, kv_heads=2, dim=24, rot_dims=0, window=3), ff=None)],
     "attention_tcgen05_head": [layer("attention", attn(heads=4, kv_heads=2, dim=64, rot_dims=16, window=100, scale=0.3), ff=None)],
+    # a projection row of more than 48 KB in 32-bit (the preparation kernel holds it in shared memory)
+    "attention_wide_projection": [layer("attention", attn(heads=40, kv_heads=10, dim=256, rot_dims=64, window=50, scale=0.05), ff=None)],
     "left_alone": [layer("parallel", pair(right_scale=0.0), ff=None)],
     "right_alone": [layer("parallel", pair(left_scale=0.0), ff=None)],
     "right_one_block_two_taps": [layer("parallel", pair(right={"width": 40, "blocks": 1, "conv": 2}, left_scale=0.0), ff=None)],
