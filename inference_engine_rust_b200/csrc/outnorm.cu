@@ -17,6 +17,56 @@ namespace {
 
 constexpr int THREADS = 256;
 
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// Rows of up to 4 * V * THREADS numbers, 16-byte accesses: every load of a row (y, x and the weight) is issued before the
+// first is used, so a row costs one round trip to memory, one block-wide sum and the stores.
+template <typename TO, int V>
+__global__ void __launch_bounds__(THREADS)
+add_normed_rows_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ w, TO* __restrict__ cast,
+                       int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  const int n4 = hidden >> 2;
+  float4 g[V], v[V], a[V];
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    g[k] = i < n4 ? *reinterpret_cast<const float4*>(w + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  const size_t r = blockIdx.x;
+  float* yr = y + r * hidden;
+  float* xr = x + r * hidden;
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    v[k] = i < n4 ? *reinterpret_cast<const float4*>(yr + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    a[k] = i < n4 ? *reinterpret_cast<const float4*>(xr + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int k = 0; k < V; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  ss = block_sum(ss, scratch);
+  const float rinv = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    if (i >= n4) continue;
+    a[k].x += v[k].x * rinv * g[k].x; a[k].y += v[k].y * rinv * g[k].y;
+    a[k].z += v[k].z * rinv * g[k].z; a[k].w += v[k].w * rinv * g[k].w;
+    *reinterpret_cast<float4*>(xr + 4 * i) = a[k];
+    *reinterpret_cast<float4*>(yr + 4 * i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (cast) store4(cast + r * hidden + 4 * i, a[k]);
+  }
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(THREADS)
 add_normed_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ w, TO* __restrict__ cast,
@@ -89,6 +139,16 @@ IERT_API int iert_add_normed(float* x, float* y, const float* w, void* cast, int
   if (rows <= 0) return IERT_OK;
   if (hidden <= 0) return IERT_BAD_ARGUMENT;
   const int vec4 = hidden % 4 == 0 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)w) & 15) == 0;
+  if (vec4 && hidden <= 4 * 8 * THREADS && (cast_dtype == IERT_F32 || cast_dtype == IERT_BF16) && ((uintptr_t)cast & 15) == 0) {
+    const int per_thread = (hidden / 4 + THREADS - 1) / THREADS;            // runs of four numbers a thread holds
+#define ROWS(TO, V) launch_dep(add_normed_rows_kernel<TO, V>, dim3(rows), dim3(THREADS), 0, stream, x, y, w, (TO*)cast, hidden, eps)
+#define PICK(TO) do { if (per_thread <= 1) ROWS(TO, 1); else if (per_thread <= 2) ROWS(TO, 2); else if (per_thread <= 4) ROWS(TO, 4); \
+                      else ROWS(TO, 8); } while (0)
+    if (cast_dtype == IERT_F32) PICK(float); else PICK(__nv_bfloat16);
+#undef PICK
+#undef ROWS
+    return iert_check_launch("add_normed");
+  }
   if (cast_dtype == IERT_F32)
     launch_dep(add_normed_kernel<float>, dim3(rows), dim3(THREADS), 0, stream, x, y, w, (float*)cast, hidden, eps, vec4);
   else if (cast_dtype == IERT_BF16)

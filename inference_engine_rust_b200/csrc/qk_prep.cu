@@ -22,7 +22,8 @@ template <typename T>
 __global__ void __launch_bounds__(THREADS)
 qk_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ qkv, IertBatchView b, IertKvView c, int heads,
                const float* __restrict__ inv_freq, int rotary_dim, int norm_mode, const float* __restrict__ wq,
-               const float* __restrict__ wk, float eps, float value_scale, int write_cache, int* __restrict__ err) {
+               const float* __restrict__ wk, float eps, float value_scale, int write_cache, int heads_per_block,
+               int* __restrict__ err) {
   extern __shared__ float sm[];
   __shared__ float scratch[33];
   pdl_launch_dependents();
@@ -38,7 +39,8 @@ qk_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ qkv
     // key's weight of zero times a NaN left in this row would still be NaN)
     pdl_wait();
     T* pad = qkv + (size_t)t * (qd + 2 * kd);
-    for (int i = threadIdx.x; i < qd + 2 * kd; i += THREADS) pad[i] = from_f32<T>(0.f);
+    if (blockIdx.y == 0)
+      for (int i = threadIdx.x; i < qd + 2 * kd; i += THREADS) pad[i] = from_f32<T>(0.f);
     return;
   }
   const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
@@ -56,11 +58,17 @@ qk_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ qkv
   T* out = qkv + (size_t)t * (qd + 2 * kd);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_heads = heads + nkv;
   constexpr int WARPS = THREADS / 32;
+  // this block's heads of [queries | keys]: [h_lo, h_hi) (few tokens: the heads of a token are spread over blocks)
+  const int h_lo = blockIdx.y * heads_per_block, h_hi = min(n_heads, h_lo + heads_per_block);
   float ssq = 0.f, ssk = 0.f;
-  for (int i = threadIdx.x; i < qd + kd; i += THREADS) {
-    const float v = pr[i];
-    row[i] = v;
-    if (i < qd) ssq = fmaf(v, v, ssq); else ssk = fmaf(v, v, ssk);
+  if (norm_mode == 1 || heads_per_block >= n_heads) {           // the whole row (its sums of squares are needed)
+    for (int i = threadIdx.x; i < qd + kd; i += THREADS) {
+      const float v = pr[i];
+      row[i] = v;
+      if (i < qd) ssq = fmaf(v, v, ssq); else ssk = fmaf(v, v, ssk);
+    }
+  } else {
+    for (int i = h_lo * hd + threadIdx.x; i < h_hi * hd; i += THREADS) row[i] = pr[i];
   }
   if (norm_mode == 1) {
     ssq = block_sum(ssq, scratch);
@@ -69,7 +77,7 @@ qk_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ qkv
     __syncthreads();
   }
   // the values: the keys as projected (a warp per head: the place in the cache is worked out once per head)
-  for (int h = warp; h < nkv; h += WARPS) {
+  for (int h = max(h_lo, heads) - heads + warp; h < h_hi - heads; h += WARPS) {
     const long long off = store ? kv_row_offset(c, slot, pos, h, err) : -1;
     const float* src = row + qd + (size_t)h * hd;
     T* dst = out + qd + kd + (size_t)h * hd;
@@ -82,7 +90,7 @@ qk_prep_kernel(const float* __restrict__ proj, long long ld, T* __restrict__ qkv
   const float rq = 1.0f / sqrtf(ssq / (float)qd + eps), rk = 1.0f / sqrtf(ssk / (float)kd + eps);
   __syncthreads();
   // per head: the whole-projection norm's factor and weight, the rotation, the unit norm, the rounding and the stores
-  for (int h = warp; h < n_heads; h += WARPS) {
+  for (int h = h_lo + warp; h < h_hi; h += WARPS) {
     float* v = row + (size_t)h * hd;
     if (norm_mode == 1) {
       const float r = h < heads ? rq : rk;
@@ -127,6 +135,10 @@ IERT_API int iert_qk_prep(const float* proj, long long ld, void* qkv, int dtype,
     return IERT_BAD_ARGUMENT;
   const size_t smem = ((size_t)(heads + cache->kv_heads) * hd + rotary_dim) * sizeof(float);
   if (smem > 200 * 1024) return IERT_BAD_ARGUMENT;
+  // many tokens: a block per token; few: the heads of a token over several blocks, a warp's worth of heads each
+  const int n_heads = heads + cache->kv_heads;
+  const int per_block = batch->n_tokens >= 256 ? n_heads : (n_heads >= 16 ? 8 : n_heads);
+  const int groups = (n_heads + per_block - 1) / per_block;
   // the opt-in for more than 48 KB of dynamic shared memory, asked once per size (and not again inside a stream capture)
 #define GO(T)                                                                                                          \
   do {                                                                                                                 \
@@ -138,8 +150,8 @@ IERT_API int iert_qk_prep(const float* proj, long long ld, void* qkv, int dtype,
       }                                                                                                                \
       allowed = smem;                                                                                                  \
     }                                                                                                                  \
-    launch_dep(qk_prep_kernel<T>, dim3(batch->n_tokens), dim3(THREADS), smem, stream, proj, ld, (T*)qkv, *batch, *cache,    \
-               heads, inv_freq, rotary_dim, norm_mode, wq, wk, eps, value_scale, write_cache, err);                      \
+    launch_dep(qk_prep_kernel<T>, dim3(batch->n_tokens, groups), dim3(THREADS), smem, stream, proj, ld, (T*)qkv, *batch,   \
+               *cache, heads, inv_freq, rotary_dim, norm_mode, wq, wk, eps, value_scale, write_cache, per_block, err);    \
   } while (0)
   if (dtype == IERT_F32) GO(float);
   else if (dtype == IERT_BF16) GO(__nv_bfloat16);

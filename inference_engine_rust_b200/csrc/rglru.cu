@@ -66,7 +66,7 @@ constexpr int CONV_TOKENS = 4, CONV_THREADS = 128;
 __global__ void __launch_bounds__(CONV_THREADS)
 rglru_conv4_kernel(const float* __restrict__ proj, long long ld, const float* __restrict__ bx,
                    const float* __restrict__ taps, const float* __restrict__ cb, const float* __restrict__ state,
-                   long long state_ld, float* __restrict__ u, int C, int K, IertBatchView b) {
+                   long long state_ld, float* __restrict__ u, int C, int K, int tokens_per_block, IertBatchView b) {
   extern __shared__ __align__(16) float taps_s[];             // [K][4 * CONV_THREADS]
   pdl_launch_dependents();
   constexpr int CH = 4 * CONV_THREADS;
@@ -82,8 +82,8 @@ rglru_conv4_kernel(const float* __restrict__ proj, long long ld, const float* __
   const float4 bias = *reinterpret_cast<const float4*>(bx + c);
   const float4 cbias = *reinterpret_cast<const float4*>(cb + c);
   pdl_wait();
-  for (int i = 0; i < CONV_TOKENS; ++i) {
-    const int t = blockIdx.x * CONV_TOKENS + i;
+  for (int i = 0; i < tokens_per_block; ++i) {
+    const int t = blockIdx.x * tokens_per_block + i;
     if (t >= b.n_tokens) break;
     const int s = sequence_of_token(b, t);
     const int slot = s < 0 ? -1 : b.slot_ids[s];
@@ -312,11 +312,26 @@ rglru_gates_tc_kernel(const float* __restrict__ u, const __nv_bfloat16* __restri
 // lanes over k, and forms the sums of up to SMALL_T tokens at a time; the weights are the traffic.
 constexpr int SMALL_T = 8;
 
+__device__ __forceinline__ void load8(const float* p, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&o)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h[e]);
+    o[2 * e] = f.x;
+    o[2 * e + 1] = f.y;
+  }
+}
+
 template <typename TW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 rglru_gates_small_kernel(const float* __restrict__ u, const TW* __restrict__ Ra, const float* __restrict__ ra_b,
                          const TW* __restrict__ Ri, const float* __restrict__ ri_b, const float* __restrict__ lam, float decay_c,
-                         float* __restrict__ A, float* __restrict__ Bv, int T, int C, int bw) {
+                         float* __restrict__ A, float* __restrict__ Bv, int T, int C, int bw, int vec8) {
   pdl_launch_dependents();
   const int ch = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (ch >= C) return;
@@ -329,24 +344,49 @@ rglru_gates_small_kernel(const float* __restrict__ u, const TW* __restrict__ Ra,
     float ar[SMALL_T], ai[SMALL_T];
 #pragma unroll
     for (int j = 0; j < SMALL_T; ++j) ar[j] = ai[j] = 0.f;
-    for (int k = lane; k < bw; k += 32) {
-      const float wr = to_f32(ra[k]), wi = to_f32(ri[k]);
+    if (vec8) {
+      // eight consecutive k per lane and pass: one 16-byte (bf16) or two (fp32) loads of either weight row, two of u per token
+      for (int k = lane * 8; k < bw; k += 256) {
+        float wr[8], wi[8];
+        load8(ra + k, wr);
+        load8(ri + k, wi);
 #pragma unroll
-      for (int j = 0; j < SMALL_T; ++j) {
-        const float uv = t0 + j < T ? u[(size_t)(t0 + j) * C + (size_t)blk * bw + k] : 0.f;
-        ar[j] = fmaf(wr, uv, ar[j]);
-        ai[j] = fmaf(wi, uv, ai[j]);
+        for (int j = 0; j < SMALL_T; ++j) {
+          if (t0 + j >= T) break;
+          const float* up = u + (size_t)(t0 + j) * C + (size_t)blk * bw + k;
+          const float4 a = *reinterpret_cast<const float4*>(up), bq = *reinterpret_cast<const float4*>(up + 4);
+          const float uv[8] = {a.x, a.y, a.z, a.w, bq.x, bq.y, bq.z, bq.w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            ar[j] = fmaf(wr[e], uv[e], ar[j]);
+            ai[j] = fmaf(wi[e], uv[e], ai[j]);
+          }
+        }
+      }
+    } else {
+      for (int k = lane; k < bw; k += 32) {
+        const float wr = to_f32(ra[k]), wi = to_f32(ri[k]);
+#pragma unroll
+        for (int j = 0; j < SMALL_T; ++j) {
+          const float uv = t0 + j < T ? u[(size_t)(t0 + j) * C + (size_t)blk * bw + k] : 0.f;
+          ar[j] = fmaf(wr, uv, ar[j]);
+          ai[j] = fmaf(wi, uv, ai[j]);
+        }
       }
     }
+    // lane j finishes token t0 + j: the sigmoids, the decay and the input term of all tokens side by side
+    float my_r = 0.f, my_i = 0.f;
 #pragma unroll
     for (int j = 0; j < SMALL_T; ++j) {
       const float sr = warp_sum(ar[j]), si = warp_sum(ai[j]);
-      if (lane == 0 && t0 + j < T) {
-        const float r = sigmoid_f(sr + rb), g = sigmoid_f(si + ib);
-        const float log_a = -decay_c * r * sp;
-        A[(size_t)(t0 + j) * C + ch] = expf(log_a);
-        Bv[(size_t)(t0 + j) * C + ch] = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f)) * g * u[(size_t)(t0 + j) * C + ch];
-      }
+      if (lane == j) { my_r = sr; my_i = si; }
+    }
+    if (lane < SMALL_T && t0 + lane < T) {
+      const size_t at = (size_t)(t0 + lane) * C + ch;
+      const float r = sigmoid_f(my_r + rb), g = sigmoid_f(my_i + ib);
+      const float log_a = -decay_c * r * sp;
+      A[at] = expf(log_a);
+      Bv[at] = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f)) * g * u[at];
     }
   }
 }
@@ -509,8 +549,9 @@ IERT_API int iert_rglru_conv(const float* proj, long long ld, const float* bx, c
   if (C % 4 == 0 && ld % 4 == 0 && state_ld % 4 == 0 &&
       (((uintptr_t)proj | (uintptr_t)bx | (uintptr_t)cb | (uintptr_t)state | (uintptr_t)u) & 15) == 0) {
     const int ch = 4 * CONV_THREADS;
-    launch_dep(rglru_conv4_kernel, dim3((batch->n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (C + ch - 1) / ch), dim3(CONV_THREADS),
-               (size_t)K * ch * sizeof(float), stream, proj, ld, bx, taps, cb, state, state_ld, u, C, K, *batch);
+    const int per = batch->n_tokens >= 256 ? CONV_TOKENS : 1;
+    launch_dep(rglru_conv4_kernel, dim3((batch->n_tokens + per - 1) / per, (C + ch - 1) / ch), dim3(CONV_THREADS),
+               (size_t)K * ch * sizeof(float), stream, proj, ld, bx, taps, cb, state, state_ld, u, C, K, per, *batch);
     return iert_check_launch("rglru_conv");
   }
   const int threads = C >= 256 ? 256 : 64;
@@ -529,12 +570,13 @@ IERT_API int iert_rglru_gates(const float* u, const void* Ra, const float* ra_b,
   if (blocks > 65535 || (bw + GO - 1) / GO > 65535) return IERT_BAD_ARGUMENT;
   if (T <= 8 * SMALL_T) {
     const dim3 g((C + 7) / 8);
+    const int vec8 = bw % 8 == 0 && (((uintptr_t)u | (uintptr_t)Ra | (uintptr_t)Ri) & 15) == 0;
     if (w_dtype == IERT_F32)
       launch_dep(rglru_gates_small_kernel<float>, g, dim3(256), 0, stream, u, (const float*)Ra, ra_b, (const float*)Ri, ri_b, lam,
-                 decay_c, A, Bv, T, C, bw);
+                 decay_c, A, Bv, T, C, bw, vec8);
     else if (w_dtype == IERT_BF16)
       launch_dep(rglru_gates_small_kernel<__nv_bfloat16>, g, dim3(256), 0, stream, u, (const __nv_bfloat16*)Ra, ra_b,
-                 (const __nv_bfloat16*)Ri, ri_b, lam, decay_c, A, Bv, T, C, bw);
+                 (const __nv_bfloat16*)Ri, ri_b, lam, decay_c, A, Bv, T, C, bw, vec8);
     else
       return IERT_BAD_ARGUMENT;
     return iert_check_launch("rglru_gates");
