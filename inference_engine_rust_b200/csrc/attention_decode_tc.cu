@@ -127,6 +127,8 @@ __device__ int balanced_parts(const IertBatchView& b, const IertKvView& c, int m
   return max(1, min(max_parts, (my_pages + per_part - 1) / per_part));
 }
 
+// CAP: the scores pass a soft cap (a kernel of its own, so that the plain path keeps its registers and instructions).
+template <bool CAP>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   extern __shared__ __align__(16) uint8_t smem[];
@@ -318,7 +320,7 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int j = jbase + n * 8 + tq * 2 + e;
-        v[n][e] = (j >= j_min && j <= pos) ? (p.cap_l2e > 0.f ? softcap_l2(sc[n][e], p.cap_k2, p.cap_l2e) : sc[n][e] * p.scale_log2e) : -INFINITY;
+        v[n][e] = (j >= j_min && j <= pos) ? (CAP ? softcap_l2(sc[n][e], p.cap_k2, p.cap_l2e) : sc[n][e] * p.scale_log2e) : -INFINITY;
         mx = fmaxf(mx, v[n][e]);
       }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -362,7 +364,7 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   }
   if (tq == 0) { ml_s[(warp * 8 + g) * 2] = m_row; ml_s[(warp * 8 + g) * 2 + 1] = l_row; }
   __syncthreads();
-  const bool direct = p.splits == 1;                  // a single split: its result is the output
+  const bool direct = p.splits == 1 && p.sink == nullptr;   // a single split: its result is the output (a sink is added by the merge kernel)
   for (int r = 0; r < n_g && r < 8; ++r) {
     float mm = -INFINITY;
     for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, ml_s[(w * 8 + r) * 2]);
@@ -372,7 +374,6 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
       wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - mm);
       ll += wgt[w] * ml_s[(w * 8 + r) * 2 + 1];
     }
-    if (direct && p.sink && mm != -INFINITY) ll += exp2f(p.sink[head0 + r] * 1.4426950408889634f - mm);
     const float inv = ll > 0.f ? 1.0f / ll : 0.f;
     for (int d = threadIdx.x; d < HD; d += THREADS) {
       float acc = 0.f;
@@ -421,7 +422,8 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
-__global__ void __launch_bounds__(TMA_THREADS)
+template <bool CAP>
+__global__ void __launch_bounds__(TMA_THREADS, 2)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             DecodeTcParams p, IertBatchView b, IertKvView c) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -646,7 +648,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int j = jbase + n * 8 + tq * 2 + e;
-        v[n][e] = (j >= j_min && j <= pos) ? (p.cap_l2e > 0.f ? softcap_l2(sc[n][e], p.cap_k2, p.cap_l2e) : sc[n][e] * p.scale_log2e) : -INFINITY;
+        v[n][e] = (j >= j_min && j <= pos) ? (CAP ? softcap_l2(sc[n][e], p.cap_k2, p.cap_l2e) : sc[n][e] * p.scale_log2e) : -INFINITY;
         mx = fmaxf(mx, v[n][e]);
       }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -713,7 +715,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
   if (tq == 0) { ml_s[(warp * 8 + g) * 2] = m_row; ml_s[(warp * 8 + g) * 2 + 1] = l_row; }
   consumer_sync();
-  const bool direct = p.splits == 1;
+  const bool direct = p.splits == 1 && p.sink == nullptr;
   for (int r = 0; r < n_g && r < 8; ++r) {
     float mm = -INFINITY;
     for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, ml_s[(w * 8 + r) * 2]);
@@ -723,7 +725,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - mm);
       ll += wgt[w] * ml_s[(w * 8 + r) * 2 + 1];
     }
-    if (direct && p.sink && mm != -INFINITY) ll += exp2f(p.sink[head0 + r] * 1.4426950408889634f - mm);
     const float inv = ll > 0.f ? 1.0f / ll : 0.f;
     for (int d = threadIdx.x; d < HD; d += THREADS) {
       float acc = 0.f;
@@ -821,7 +822,8 @@ int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const 
   if (merge > smem) smem = merge;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attention_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(attention_decode_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_decode_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       cudaGetLastError();
       return IERT_CUDA_ERROR;
     }
@@ -840,22 +842,32 @@ int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const 
     if (merge > ring) smem_tma += merge - ring;
     static bool configured_tma = false;
     if (!configured_tma) {
-      if (cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tma) != cudaSuccess) {
+      if (cudaFuncSetAttribute(attention_decode_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tma) != cudaSuccess ||
+          cudaFuncSetAttribute(attention_decode_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tma) != cudaSuccess) {
         cudaGetLastError();
         return IERT_CUDA_ERROR;
       }
       configured_tma = true;
     }
-    launch_dep(attention_decode_tma_kernel, dim3(cache->kv_heads * p.slices, T, splits), dim3(TMA_THREADS), smem_tma, stream,
-               map_k, map_v, p, *batch, *cache);
+    if (p.cap_l2e > 0.f)
+      launch_dep(attention_decode_tma_kernel<true>, dim3(cache->kv_heads * p.slices, T, splits), dim3(TMA_THREADS), smem_tma, stream,
+                 map_k, map_v, p, *batch, *cache);
+    else
+      launch_dep(attention_decode_tma_kernel<false>, dim3(cache->kv_heads * p.slices, T, splits), dim3(TMA_THREADS), smem_tma, stream,
+                 map_k, map_v, p, *batch, *cache);
     launched = true;
   }
 #endif
-  if (!launched)
-    launch_dep(attention_decode_tc_kernel, dim3(cache->kv_heads * p.slices, T, splits), dim3(THREADS), smem, stream,
-               p, *batch, *cache);
+  if (!launched) {
+    if (p.cap_l2e > 0.f)
+      launch_dep(attention_decode_tc_kernel<true>, dim3(cache->kv_heads * p.slices, T, splits), dim3(THREADS), smem, stream,
+                 p, *batch, *cache);
+    else
+      launch_dep(attention_decode_tc_kernel<false>, dim3(cache->kv_heads * p.slices, T, splits), dim3(THREADS), smem, stream,
+                 p, *batch, *cache);
+  }
   if (cudaGetLastError() != cudaSuccess) return IERT_CUDA_ERROR;
-  if (splits == 1) return IERT_OK;                   // nothing to merge: the kernel wrote the output
+  if (splits == 1 && !sink) return IERT_OK;          // nothing to merge: the kernel wrote the output
   launch_dep(attention_decode_tc_combine_kernel, dim3(T, heads), dim3(HD >= 128 ? 128 : 64), 0, stream, p, *batch, *cache);
   return cudaGetLastError() == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
 }

@@ -507,7 +507,7 @@ def attention_decode_tc(qkv, out, batch: BatchView, kv: KvView, heads: int, scal
     if status != 0:
         raise KernelError("attention_decode_tc: the launch failed")
     global launch_count
-    launch_count += 1 if splits == 1 else 2        # a single split needs no merge kernel
+    launch_count += 1 if splits == 1 and sink is None else 2        # a single split without a sink needs no merge kernel
     return True
 
 
